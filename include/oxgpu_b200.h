@@ -1,0 +1,235 @@
+/* oxgpu_b200 -- C ABI of the B200 (sm_100a) dense GEMM path.
+ *
+ * Plain C: pointers, sizes and ints only.  Every function returns a status:
+ *   0   success
+ *  <0   contract violation detected on the host before any launch (OXGPU_E_*)
+ *  >0   a CUDA runtime/driver error code (cudaError_t / CUresult value)
+ * oxgpu_b200_last_error() returns a thread-local message for the last non-zero
+ * status.  Nothing here synchronises the device unless the comment says so;
+ * launches go to the stream passed in (NULL = the legacy default stream).
+ *
+ * "Reference" below is the OxCaml compiler project this library is a drop-in
+ * for; citations are path:line inside that project.  Both operands are
+ * K-contiguous exactly as in the reference: A is [M,K] row-major and B is
+ * supplied transposed as B^T [N,K] row-major (test/hardware/run_gemm_h100.cu:
+ * 137-148, bench/bench.py:265-271).  C is f32 [M,N] row-major and is
+ * overwritten (no alpha/beta), examples/kernels/gemm.ml:147-161.
+ */
+#ifndef OXGPU_B200_H
+#define OXGPU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define OXGPU_API __attribute__((visibility("default")))
+#else
+#define OXGPU_API
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  OXGPU_OK = 0,
+  OXGPU_E_INVALID_ARG = -1,    /* null pointer, non-positive dimension, bad enum */
+  OXGPU_E_CONFIG = -2,         /* tile_config rejected by validate / parse_config */
+  OXGPU_E_UNKNOWN_KERNEL = -3, /* no catalog entry of that name / for that tile */
+  OXGPU_E_SHAPE = -4,          /* M, N or K not divisible as the entry point requires */
+  OXGPU_E_ALIGN = -5,          /* pointer or leading dimension not 16-byte aligned */
+  OXGPU_E_TOO_LARGE = -6,      /* exceeds a documented maximum */
+  OXGPU_E_DEVICE_TIMEOUT = -7, /* a bounded device-side wait ran out (see device_status) */
+  OXGPU_E_NO_DRIVER = -8       /* the CUDA driver entry points could not be resolved */
+};
+
+OXGPU_API const char *oxgpu_b200_last_error(void);
+OXGPU_API const char *oxgpu_b200_strerror(int status);
+
+/* ---- tile catalog: test/gemm_catalog.ml -------------------------------- */
+
+/* type tile_config (test/gemm_catalog.ml:9-15). */
+typedef struct oxgpu_tile_config {
+  int bm, bn, bk, stages, producers;
+} oxgpu_tile_config;
+
+/* warp_groups / consumers / threads (test/gemm_catalog.ml:17-19): the
+ * reference's Hopper CTA width, kept for catalog parity.  The B200 kernels'
+ * own launch facts come from oxgpu_b200_kernel_info. */
+OXGPU_API int oxgpu_b200_config_threads(const oxgpu_tile_config *c);
+
+/* validate (test/gemm_catalog.ml:21-35).  Returns OXGPU_E_CONFIG with the
+ * reference's invalid_arg text in last_error on rejection. */
+OXGPU_API int oxgpu_b200_validate_config(const oxgpu_tile_config *c);
+
+/* string_of_config (test/gemm_catalog.ml:37-40):
+ * "bm=..,bn=..,bk=..,stages=..,producers=..,threads=..".  Writes at most cap
+ * bytes including the terminator. */
+OXGPU_API int oxgpu_b200_string_of_config(const oxgpu_tile_config *c, char *buf, size_t cap);
+
+/* parse_config (test/gemm_catalog.ml:42-73): comma-separated key=value, keys
+ * bm bn bk producers required, stages defaults to 3, unknown keys ignored,
+ * result validated. */
+OXGPU_API int oxgpu_b200_parse_config(const char *spec, oxgpu_tile_config *out);
+
+/* tile_catalog (test/gemm_catalog.ml:80-89) in order; entry 0 is the fallback
+ * tile hopper_f32 (92-95). */
+OXGPU_API int oxgpu_b200_catalog_size(void);
+OXGPU_API int oxgpu_b200_catalog_get(int index, oxgpu_tile_config *out);
+
+/* kernel_binding (test/gemm_catalog.ml:101-112): tile -> entry symbol of
+ * examples/kernels/gemm.ml:165-199 ("gemm_fast", "gemm_bm128_bn256_s3", ...). */
+OXGPU_API int oxgpu_b200_kernel_binding(const oxgpu_tile_config *c, const char **name);
+
+/* choose_config ?m ?n ?k (test/gemm_catalog.ml:114-137): size -> tile. */
+OXGPU_API int oxgpu_b200_choose_config(int m, int n, int k, oxgpu_tile_config *out);
+
+/* `emit_gemm_ptx --info` (test/emit_gemm_ptx.ml:39-43): launch facts of a
+ * catalog entry.  Reports the B200 kernel that serves `name`: CTA width,
+ * dynamic shared bytes and total shared bytes.  `name` is one of the ten
+ * entry symbols (examples/kernels/gemm.ml:165-199, gemm_bf16.ml:130-132). */
+OXGPU_API int oxgpu_b200_kernel_info(const char *name, int *threads, int *dynamic_smem,
+                                     int *total_smem);
+
+/* Tile and input width a catalog entry was specialised for
+ * (examples/kernels/gemm.ml:165-199): element_bytes 4 = f32/TF32, 2 = bf16. */
+OXGPU_API int oxgpu_b200_kernel_tile(const char *name, oxgpu_tile_config *tile, int *element_bytes);
+
+/* Gpu.grouped_tile_m / grouped_tile_n (tools/exporter/export_prims_index.ml:
+ * 40-61; used at examples/kernels/gemm.ml:73-75): the grouped CTA order as a
+ * pure function of the linear tile id, the one the persistent scheduler uses. */
+OXGPU_API int oxgpu_b200_grouped_tile(int pid, int group, int tiles_m, int tiles_n, int *tile_m,
+                                      int *tile_n);
+
+/* ---- host launch layer: test/hardware/run_gemm_h100.cu, bench/bench.py -- */
+
+/* encode_tiled_2d (test/hardware/run_gemm_h100.cu:46-72) /
+ * encode_tensor_map_2d (bench/bench.py:126-147): 2-D tiled map, 128-byte
+ * swizzle, L2 promotion 128 B, no out-of-bounds fill (zeros).  element_bytes 4
+ * -> FLOAT32, 2 -> BFLOAT16.  map_out receives the 128-byte CUtensorMap
+ * (host memory, 64-byte aligned). */
+OXGPU_API int oxgpu_b200_encode_tmap_2d(void *map_out, const void *device_ptr, int element_bytes,
+                                        uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
+                                        uint32_t box0, uint32_t box1);
+
+/* The catalog entry points themselves -- `.visible .entry <name>(a_tmap,
+ * b_tmap, c, m, n, k)` (lib/backend/ptx.ml:91-109), launched by
+ * test/hardware/run_gemm_h100.cu:183-185 and bench/bench.py:281-292.
+ * a_tmap / b_tmap are DEVICE pointers to 128-byte CUtensorMaps encoded as the
+ * reference encodes them: A dims (K,M) box (BK,bm), B^T dims (K,N) box
+ * (BK,bn) for the tile `name` was specialised for, 128-byte swizzle.  c is a
+ * device f32 pointer with row stride (n/bn)*bn = n.  Requires m % bm == 0,
+ * n % bn == 0, k % BK == 0 like the reference (bench/bench.py:247-250); BK is
+ * 32 for the f32 entries and 64 for gemm_bf16_fast.  The library serves every
+ * name with a 128-row (or 256-row) tcgen05 tile; bm=64 entries therefore also
+ * need m % 128 == 0.  Replaces cuLaunchKernel(fn, n/bn, m/bm, 1, threads, ...). */
+OXGPU_API int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uint64_t c,
+                                   int m, int n, int k, void *stream);
+
+/* Variant selection for the buffer entry points (flags argument). */
+enum {
+  OXGPU_VARIANT_AUTO = 0,
+  OXGPU_VARIANT_1CTA_128x256 = 1, /* one CTA, UMMA 128x256 */
+  OXGPU_VARIANT_1CTA_128x128 = 2,
+  OXGPU_VARIANT_1CTA_256x128 = 3, /* one CTA, two UMMA 128x128 sharing B */
+  OXGPU_VARIANT_2CTA_256x256 = 4, /* CTA pair, cta_group::2 UMMA 256x256 */
+  OXGPU_VARIANT_2CTA_256x128 = 5,
+  OXGPU_VARIANT_SPLITK = 6        /* 1-CTA 128x128 tiles over K slices + reduce; needs workspace */
+};
+#define OXGPU_FLAG_VARIANT(v) ((unsigned)(v) & 0xffu)
+#define OXGPU_FLAG_STAGES(s) (((unsigned)(s) & 0xfu) << 8)    /* 0 = deepest that fits */
+#define OXGPU_FLAG_GROUP_M(g) (((unsigned)(g) & 0xffu) << 12) /* 0 = 16, the reference's */
+#define OXGPU_FLAG_SPLITS(s) (((unsigned)(s) & 0xffu) << 20)  /* 0 = chosen by the library */
+
+/* Buffer entry points: the library encodes its own maps, so it may pick any
+ * variant (2-CTA tiles, ragged edges).  a: [M,K] row-major with leading
+ * dimension lda (elements); bt: B^T [N,K] with ldb; c: f32 [M,N] with ldc.
+ * Pointers 16-byte aligned, lda*esize, ldb*esize and ldc*4 multiples of 16.
+ * M and N may be ragged; K must make K*esize a multiple of 16.
+ * hopper_gemm (examples/kernels/gemm.ml:47-163): TF32-rounded f32 inputs.
+ * hopper_gemm_bf16 (examples/kernels/gemm_bf16.ml:33-128): bf16 inputs. */
+OXGPU_API int oxgpu_b200_gemm_tf32(const float *a, const float *bt, float *c, int m, int n, int k,
+                                   int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
+                                   void *stream);
+OXGPU_API int oxgpu_b200_gemm_bf16(const uint16_t *a, const uint16_t *bt, float *c, int m, int n,
+                                   int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
+                                   void *stream);
+
+/* Same, with caller-provided scratch for OXGPU_VARIANT_SPLITK (f32 partial
+ * tiles).  workspace_bytes must be at least
+ * oxgpu_b200_splitk_workspace_bytes(m, n, splits). */
+OXGPU_API size_t oxgpu_b200_splitk_workspace_bytes(int m, int n, int splits);
+OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, float *c, int m,
+                                      int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                      unsigned flags, void *workspace, size_t workspace_bytes,
+                                      void *stream);
+
+/* Exact GEMM on CUDA cores: one f32 accumulator per output, k ascending, a
+ * rounded multiply then a rounded add (never fused) -- the arithmetic of the
+ * host reference loop (test/hardware/run_gemm_h100.cu:150-162), so the result
+ * is bit-identical to that loop.  input_mode: 0 = f32 operands as they are
+ * (the path for f32 inputs that must meet the strict 1e-5*sqrt(K) bound),
+ * 1 = f32 operands truncated to TF32 first (run_gemm_h100.cu:40-44),
+ * 2 = bf16-bit operands widened exactly (32-36).  Also the full-matrix checker
+ * for shapes too large for a CPU loop.  lda/ldb/ldc in elements; any M, N, K. */
+OXGPU_API int oxgpu_b200_gemm_exact(const void *a, const void *bt, float *c, int m, int n, int k,
+                                    int64_t lda, int64_t ldb, int64_t ldc, int input_mode,
+                                    void *stream);
+
+/* B[K,N] row-major -> B^T[N,K] row-major on the device, the re-layout the
+ * reference performs on the host outside timing (run_gemm_h100.cu:142-148,
+ * bench/bench.py:268).  element_bytes 2 or 4. */
+OXGPU_API int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_bytes,
+                                   void *stream);
+
+/* f32 -> bf16 bits, round-to-nearest-even (run_gemm_h100.cu:26-30). */
+OXGPU_API int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *stream);
+
+/* Host-buffer entry point: A, B^T and C live in HOST memory (pinned or
+ * pageable).  Uploads the operands, runs gemm_bf16 and downloads C, pipelined
+ * over row blocks of A/C on internal streams; returns after C is complete on
+ * the host (this call synchronises).  Device staging buffers are allocated on
+ * first use and cached per device; oxgpu_b200_release_staging frees them. */
+OXGPU_API int oxgpu_b200_gemm_bf16_host(const uint16_t *a_host, const uint16_t *bt_host,
+                                        float *c_host, int m, int n, int k, unsigned flags);
+OXGPU_API int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *c_host,
+                                        int m, int n, int k, unsigned flags);
+OXGPU_API int oxgpu_b200_release_staging(void);
+
+/* ---- synthetic operands -------------------------------------------------- */
+/* Counter-based generator, value = f(seed, linear index): uniform on [-1,1)
+ * (f32) or normal(0,std) (f32 or bf16 bits).  dtype: 4 = f32, 2 = bf16. */
+OXGPU_API int oxgpu_b200_fill_uniform(void *dst, size_t count, int element_bytes, uint32_t seed,
+                                      uint64_t index_offset, void *stream);
+OXGPU_API int oxgpu_b200_fill_normal(void *dst, size_t count, int element_bytes, uint32_t seed,
+                                     float std, uint64_t index_offset, void *stream);
+
+/* ---- device status ------------------------------------------------------- */
+/* Every device-side wait (mbarrier, TMEM hand-off) has a spin budget.  When
+ * one runs out the CTA records {code, block, stage/tile, parity} in a
+ * per-device status block and leaves through the normal exit path.  This call
+ * synchronises the device, copies the block out (words[0] != 0 means a wait
+ * timed out since the last clear) and clears it.  Returns
+ * OXGPU_E_DEVICE_TIMEOUT in that case.  The reference's waits are unbounded
+ * (lib/backend/ptx.ml:174-181). */
+OXGPU_API int oxgpu_b200_device_status(uint32_t words[8]);
+
+/* Number of kernels this library has launched in this process (all entry
+ * points), for accounting. */
+OXGPU_API uint64_t oxgpu_b200_launch_count(void);
+
+/* Runs the bounded-wait self test: one CTA waits, with the given budget, on a
+ * barrier that nothing arrives on.  The wait must give up, the kernel must
+ * return normally, and the status block must say so: returns
+ * OXGPU_E_DEVICE_TIMEOUT when that happened (the expected outcome), OXGPU_OK
+ * if the wait did not time out.  Synchronises the device. */
+OXGPU_API int oxgpu_b200_selftest_bounded_wait(uint64_t budget_ns);
+
+/* Library build facts: "sm_100a", CUDA runtime version, variants compiled. */
+OXGPU_API const char *oxgpu_b200_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXGPU_B200_H */

@@ -1,0 +1,656 @@
+// C-ABI launch layer: argument contracts, tensor-map encoding, variant choice
+// and kernel launches.  Host-side counterpart of the reference's launcher
+// (test/hardware/run_gemm_h100.cu:46-72,119-122,164-186; bench/bench.py:
+// 126-156,266-292).  There is no CPU fallback anywhere in this file: every
+// compute entry point either launches a CUDA kernel or returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "common.hpp"
+#include "umma_gemm.cuh"
+#include "util_kernels.cuh"
+
+namespace oxgpu {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int kKinds = 2;     // 0 = bf16, 1 = tf32
+constexpr int kVariants = 6;  // index by Variant value (1..5 used)
+
+std::atomic<uint64_t> g_launches{0};
+
+struct Staging {
+  void *a = nullptr, *bt = nullptr, *c = nullptr;
+  size_t a_bytes = 0, bt_bytes = 0, c_bytes = 0;
+  cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
+  cudaEvent_t bt_ready = nullptr;
+  cudaEvent_t a_ready[64] = {}, c_ready[64] = {};
+  bool events = false;
+};
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  bool attr_set[kKinds][kVariants] = {};
+  int max_clusters[kKinds][kVariants] = {};
+  Staging staging;
+};
+
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mutex;          // lazy per-device and driver-entry set-up
+std::mutex g_staging_mutex;  // host-buffer entry points (one at a time)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int cuda_fail(cudaError_t e, const char *what) {
+  return fail((int)e, std::string(what) + ": " + cudaGetErrorName(e) + ": " + cudaGetErrorString(e));
+}
+
+#define OX_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e_ = (call);                            \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call); \
+  } while (0)
+
+int resolve_driver() {
+  if (g_encode) return OXGPU_OK;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_encode) return OXGPU_OK;
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000,
+                                                   cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+    cudaGetLastError();
+    return fail(OXGPU_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  }
+  g_encode = (EncodeTiledFn)fn;
+  return OXGPU_OK;
+}
+
+int current_device(int *dev, DeviceState **state) {
+  OX_CUDA(cudaGetDevice(dev));
+  if (*dev < 0 || *dev >= kMaxDevices) return fail(OXGPU_E_INVALID_ARG, "device index out of range");
+  DeviceState &s = g_dev[*dev];
+  if (!s.ready) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!s.ready) {
+      OX_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, *dev));
+      int major = 0;
+      OX_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, *dev));
+      if (major != 10)
+        return fail(OXGPU_E_INVALID_ARG,
+                    "this library is built for sm_100a only; the current device is not a B200-class GPU");
+      s.ready = true;
+    }
+  }
+  *state = &s;
+  return OXGPU_OK;
+}
+
+int encode_2d(CUtensorMap *map, const void *ptr, int element_bytes, uint64_t dim0, uint64_t dim1,
+              uint64_t stride1_bytes, uint32_t box0, uint32_t box1) {
+  int st = resolve_driver();
+  if (st) return st;
+  CUtensorMapDataType dt;
+  if (element_bytes == 4) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  else if (element_bytes == 2) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  else return fail(OXGPU_E_INVALID_ARG, "element_bytes must be 2 (bf16) or 4 (f32)");
+  cuuint64_t dims[2] = {dim0, dim1};
+  cuuint64_t strides[1] = {stride1_bytes};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char text[200];
+    std::snprintf(text, sizeof text,
+                  "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu x %llu, stride %llu, box %u x %u)",
+                  (int)r, (unsigned long long)dim0, (unsigned long long)dim1,
+                  (unsigned long long)stride1_bytes, box0, box1);
+    return fail((int)r, text);
+  }
+  return OXGPU_OK;
+}
+
+const void *kernel_for(int kind, int variant) {
+#define OX_K(K, BM, BN, CG) ((const void *)umma_gemm_kernel<K, BM, BN, CG>)
+  if (kind == 0) {
+    switch (variant) {
+      case VARIANT_1CTA_128x256: return OX_K(0, 128, 256, 1);
+      case VARIANT_1CTA_128x128: return OX_K(0, 128, 128, 1);
+      case VARIANT_1CTA_256x128: return OX_K(0, 256, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_K(0, 128, 256, 2);
+      case VARIANT_2CTA_256x128: return OX_K(0, 128, 128, 2);
+    }
+  } else {
+    switch (variant) {
+      case VARIANT_1CTA_128x256: return OX_K(1, 128, 256, 1);
+      case VARIANT_1CTA_128x128: return OX_K(1, 128, 128, 1);
+      case VARIANT_1CTA_256x128: return OX_K(1, 256, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_K(1, 128, 256, 2);
+      case VARIANT_2CTA_256x128: return OX_K(1, 128, 128, 2);
+    }
+  }
+#undef OX_K
+  return nullptr;
+}
+
+unsigned long long wait_budget_ns() {
+  static unsigned long long v = [] {
+    const char *e = std::getenv("OXGPU_WAIT_BUDGET_MS");
+    double ms = e ? std::atof(e) : 5000.0;
+    if (!(ms > 0)) ms = 5000.0;
+    return (unsigned long long)(ms * 1e6);
+  }();
+  return v;
+}
+
+struct LaunchPlan {
+  int kind, variant, stages, group_m;
+  int splits, kb_per_split, split_row_stride;
+};
+
+// Launch one tcgen05 GEMM.  Maps are either inside `p` (by value) or behind
+// p.a_map_ptr / p.b_map_ptr.
+int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, int n, int k,
+                cudaStream_t stream) {
+  const VariantShape shape = variant_shape(plan.variant);
+  const void *fn = kernel_for(plan.kind, plan.variant);
+  if (!fn || shape.cta_group == 0) return fail(OXGPU_E_INVALID_ARG, "unknown kernel variant");
+  int stages = plan.stages;
+  const int most = variant_max_stages(plan.variant);
+  if (stages <= 0 || stages > most) stages = most;
+  if (stages < 2) stages = 2;
+  const int smem = variant_smem_bytes(plan.variant, stages);
+
+  const int kbe = plan.kind == 0 ? 64 : 32;
+  p.tiles_m = (m + shape.tile_m - 1) / shape.tile_m;
+  p.tiles_n = (n + shape.tile_n - 1) / shape.tile_n;
+  p.num_k_blocks = (k + kbe - 1) / kbe;
+  p.stages = stages;
+  p.group_m = plan.group_m > 0 ? plan.group_m : 16;
+  p.k_block_elems = kbe;
+  p.splits = plan.splits > 0 ? plan.splits : 1;
+  p.kb_per_split = plan.splits > 1 ? plan.kb_per_split : p.num_k_blocks;
+  p.split_row_stride = plan.split_row_stride;
+  p.wait_budget_ns = wait_budget_ns();
+
+  bool &attr = dev.attr_set[plan.kind][plan.variant];
+  if (!attr) {
+    OX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
+    attr = true;
+  }
+
+  const long long work = (long long)p.tiles_m * p.tiles_n * p.splits;
+  if (work <= 0 || work > 0x7fffffffLL) return fail(OXGPU_E_TOO_LARGE, "too many tiles");
+
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof cfg);
+  cfg.blockDim = dim3(kThreadsPerCta, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  if (shape.cta_group == 2) {
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    int &maxc = dev.max_clusters[plan.kind][plan.variant];
+    if (maxc == 0) {
+      cfg.gridDim = dim3(2 * (dev.sm_count / 2), 1, 1);
+      int nc = 0;
+      OX_CUDA(cudaOccupancyMaxActiveClusters(&nc, fn, &cfg));
+      if (nc <= 0) return fail(OXGPU_E_INVALID_ARG, "no CTA pair of this variant fits on the device");
+      maxc = nc;
+    }
+    long long clusters = work < maxc ? work : maxc;
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  } else {
+    long long ctas = work < dev.sm_count ? work : dev.sm_count;
+    cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+  }
+  void *args[1] = {(void *)&p};
+  OX_CUDA(cudaLaunchKernelExC(&cfg, fn, args));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_buffers(const void *a, const void *bt, const float *c, int m, int n, int k, int64_t lda,
+                  int64_t ldb, int64_t ldc, int esize) {
+  if (!a || !bt || !c) return fail(OXGPU_E_INVALID_ARG, "null operand pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(OXGPU_E_INVALID_ARG, "M, N and K must be positive");
+  if (lda < k || ldb < k || ldc < n)
+    return fail(OXGPU_E_INVALID_ARG, "leading dimension smaller than the row length");
+  if (!aligned16(a) || !aligned16(bt) || !aligned16(c))
+    return fail(OXGPU_E_ALIGN, "operand pointers must be 16-byte aligned");
+  if ((lda * esize) % 16 || (ldb * esize) % 16 || (ldc * 4) % 16)
+    return fail(OXGPU_E_ALIGN, "leading dimensions must be multiples of 16 bytes");
+  if (((int64_t)k * esize) % 16)
+    return fail(OXGPU_E_SHAPE, "K must make a row a multiple of 16 bytes (8 bf16 / 4 f32)");
+  return OXGPU_OK;
+}
+
+// Variant choice for the buffer entry points.  Large problems take the CTA-pair
+// 256x256 tile (least shared-memory and L2 traffic per flop); problems with few
+// tiles fall back to smaller tiles so more SMs have work.
+int choose_variant(const DeviceState &dev, int m, int n, int k) {
+  (void)k;
+  auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
+  const int pairs = dev.sm_count / 2;
+  if (tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
+  if (tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
+  if (tiles(128, 256) >= dev.sm_count / 2) return VARIANT_1CTA_128x256;
+  return VARIANT_1CTA_128x128;
+}
+
+int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
+                 int64_t ldb, int64_t ldc, unsigned flags, void *workspace, size_t workspace_bytes,
+                 cudaStream_t stream) {
+  const int esize = kind == 0 ? 2 : 4;
+  int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, esize);
+  if (st) return st;
+  int dev_index;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+
+  int variant = (int)(flags & 0xffu);
+  const int stages = (int)((flags >> 8) & 0xfu);
+  const int group_m = (int)((flags >> 12) & 0xffu);
+  int splits = (int)((flags >> 20) & 0xffu);
+  const bool splitk = variant == VARIANT_SPLITK;
+  if (variant == VARIANT_AUTO) variant = choose_variant(*dev, m, n, k);
+  if (splitk) variant = VARIANT_1CTA_128x128;
+  if (variant < VARIANT_1CTA_128x256 || variant > VARIANT_2CTA_256x128)
+    return fail(OXGPU_E_INVALID_ARG, "unknown variant in flags");
+  const VariantShape shape = variant_shape(variant);
+  const int kbe = kind == 0 ? 64 : 32;
+
+  LaunchPlan plan{kind, variant, stages, group_m, 1, 0, 0};
+  GemmParams p;
+  std::memset(&p, 0, sizeof p);
+  const int a_box = shape.cta_a_rows, b_box = shape.cta_b_rows;
+  p.a_box_rows = a_box;
+  p.b_box_rows = b_box;
+  if ((st = encode_2d(&p.map_a, a, esize, (uint64_t)k, (uint64_t)m, (uint64_t)lda * esize, kbe, a_box)))
+    return st;
+  if ((st = encode_2d(&p.map_b, bt, esize, (uint64_t)k, (uint64_t)n, (uint64_t)ldb * esize, kbe, b_box)))
+    return st;
+
+  if (!splitk) {
+    if ((st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32)))
+      return st;
+    return launch_umma(*dev, plan, p, m, n, k, stream);
+  }
+
+  // split-K: partial tiles go to the workspace [splits][m_pad][n4*4], then a
+  // deterministic reduction writes C.
+  if (n % 4) return fail(OXGPU_E_SHAPE, "split-K needs N to be a multiple of 4");
+  const int num_kb = (k + kbe - 1) / kbe;
+  if (splits <= 0) {
+    long long tiles = (long long)((m + 127) / 128) * ((n + 127) / 128);
+    splits = (int)((2LL * dev->sm_count + tiles - 1) / tiles);
+    if (splits > 16) splits = 16;
+  }
+  if (splits > num_kb) splits = num_kb;
+  if (splits < 1) splits = 1;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;  // every slice gets at least one K block
+  const int m_pad = ((m + 127) / 128) * 128;
+  const size_t need = (size_t)splits * m_pad * (size_t)n * sizeof(float);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(OXGPU_E_INVALID_ARG, "split-K workspace missing, misaligned or too small");
+  if ((st = encode_2d(&p.map_c, workspace, 4, (uint64_t)n, (uint64_t)splits * m_pad, (uint64_t)n * 4,
+                      32, 32)))
+    return st;
+  plan.splits = splits;
+  plan.kb_per_split = kb_per;
+  plan.split_row_stride = m_pad;
+  if ((st = launch_umma(*dev, plan, p, m, n, k, stream))) return st;
+  const size_t total = (size_t)m * (n / 4);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > dev->sm_count * 8) blocks = dev->sm_count * 8;
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>((const float4 *)workspace, c, m, n, ldc, splits,
+                                                   (int64_t)m_pad);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+int ensure_staging(Staging &s, size_t a_bytes, size_t bt_bytes, size_t c_bytes) {
+  if (!s.in) {
+    OX_CUDA(cudaStreamCreateWithFlags(&s.in, cudaStreamNonBlocking));
+    OX_CUDA(cudaStreamCreateWithFlags(&s.compute, cudaStreamNonBlocking));
+    OX_CUDA(cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking));
+  }
+  if (!s.events) {
+    OX_CUDA(cudaEventCreateWithFlags(&s.bt_ready, cudaEventDisableTiming));
+    for (int i = 0; i < 64; i++) {
+      OX_CUDA(cudaEventCreateWithFlags(&s.a_ready[i], cudaEventDisableTiming));
+      OX_CUDA(cudaEventCreateWithFlags(&s.c_ready[i], cudaEventDisableTiming));
+    }
+    s.events = true;
+  }
+  auto grow = [](void **ptr, size_t *have, size_t want) -> cudaError_t {
+    if (*have >= want) return cudaSuccess;
+    if (*ptr) {
+      cudaError_t e = cudaFree(*ptr);
+      if (e != cudaSuccess) return e;
+      *ptr = nullptr;
+      *have = 0;
+    }
+    cudaError_t e = cudaMalloc(ptr, want);
+    if (e == cudaSuccess) *have = want;
+    return e;
+  };
+  OX_CUDA(grow(&s.a, &s.a_bytes, a_bytes));
+  OX_CUDA(grow(&s.bt, &s.bt_bytes, bt_bytes));
+  OX_CUDA(grow(&s.c, &s.c_bytes, c_bytes));
+  return OXGPU_OK;
+}
+
+// Host-buffer GEMM: B^T goes up once; A goes up, C is computed and comes down
+// in row blocks, with upload, compute and download on three streams so the two
+// copy directions and the math overlap.
+int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, int m, int n, int k,
+              unsigned flags) {
+  const int esize = kind == 0 ? 2 : 4;
+  if (!a_host || !bt_host || !c_host) return fail(OXGPU_E_INVALID_ARG, "null host pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(OXGPU_E_INVALID_ARG, "M, N and K must be positive");
+  if (((int64_t)k * esize) % 16 || n % 4)
+    return fail(OXGPU_E_SHAPE, "rows of A/B^T must be multiples of 16 bytes and N a multiple of 4");
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  Staging &s = dev->staging;
+  std::lock_guard<std::mutex> lock(g_staging_mutex);
+  const size_t a_bytes = (size_t)m * k * esize, bt_bytes = (size_t)n * k * esize;
+  const size_t c_bytes = (size_t)m * n * sizeof(float);
+  if ((st = ensure_staging(s, a_bytes, bt_bytes, c_bytes))) return st;
+
+  // Row blocks: multiples of 256 rows, at most 64 blocks, about 8 per problem.
+  int block_rows = ((m / 8 + 255) / 256) * 256;
+  if (block_rows < 256) block_rows = 256;
+  while ((m + block_rows - 1) / block_rows > 64) block_rows *= 2;
+  const int blocks = (m + block_rows - 1) / block_rows;
+
+  OX_CUDA(cudaMemcpyAsync(s.bt, bt_host, bt_bytes, cudaMemcpyHostToDevice, s.in));
+  OX_CUDA(cudaEventRecord(s.bt_ready, s.in));
+  OX_CUDA(cudaStreamWaitEvent(s.compute, s.bt_ready, 0));
+  for (int b = 0; b < blocks; b++) {
+    const int r0 = b * block_rows;
+    const int rows = m - r0 < block_rows ? m - r0 : block_rows;
+    const char *a_src = (const char *)a_host + (size_t)r0 * k * esize;
+    char *a_dst = (char *)s.a + (size_t)r0 * k * esize;
+    OX_CUDA(cudaMemcpyAsync(a_dst, a_src, (size_t)rows * k * esize, cudaMemcpyHostToDevice, s.in));
+    OX_CUDA(cudaEventRecord(s.a_ready[b], s.in));
+    OX_CUDA(cudaStreamWaitEvent(s.compute, s.a_ready[b], 0));
+    float *c_dst = (float *)s.c + (size_t)r0 * n;
+    if ((st = gemm_buffers(kind, a_dst, s.bt, c_dst, rows, n, k, k, k, n, flags, nullptr, 0,
+                           s.compute)))
+      return st;
+    OX_CUDA(cudaEventRecord(s.c_ready[b], s.compute));
+    OX_CUDA(cudaStreamWaitEvent(s.out, s.c_ready[b], 0));
+    OX_CUDA(cudaMemcpyAsync(c_host + (size_t)r0 * n, c_dst, (size_t)rows * n * sizeof(float),
+                            cudaMemcpyDeviceToHost, s.out));
+  }
+  OX_CUDA(cudaStreamSynchronize(s.out));
+  OX_CUDA(cudaStreamSynchronize(s.in));
+  return OXGPU_OK;
+}
+
+}  // namespace
+}  // namespace oxgpu
+
+using namespace oxgpu;
+
+extern "C" {
+
+int oxgpu_b200_encode_tmap_2d(void *map_out, const void *device_ptr, int element_bytes,
+                              uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes, uint32_t box0,
+                              uint32_t box1) {
+  if (!map_out || !device_ptr) return fail(OXGPU_E_INVALID_ARG, "null argument");
+  if ((reinterpret_cast<uintptr_t>(map_out) & 63u) != 0)
+    return fail(OXGPU_E_ALIGN, "a CUtensorMap must be 64-byte aligned");
+  return encode_2d((CUtensorMap *)map_out, device_ptr, element_bytes, dim0, dim1, stride1_bytes, box0,
+                   box1);
+}
+
+int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uint64_t c, int m,
+                         int n, int k, void *stream) {
+  const CatalogEntry *e = find_entry(name);
+  if (!e) return fail(OXGPU_E_UNKNOWN_KERNEL, std::string("no kernel named ") + (name ? name : "(null)"));
+  if (!a_tmap || !b_tmap || !c) return fail(OXGPU_E_INVALID_ARG, "null device pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(OXGPU_E_INVALID_ARG, "M, N and K must be positive");
+  if ((a_tmap & 63u) || (b_tmap & 63u))
+    return fail(OXGPU_E_ALIGN, "tensor maps must be 64-byte aligned in device memory");
+  if (c & 15u) return fail(OXGPU_E_ALIGN, "C must be 16-byte aligned");
+  const oxgpu_tile_config &t = e->tile;
+  // The reference refuses these sizes before launching (bench/bench.py:247-250).
+  if (m % t.bm || n % t.bn || k % t.bk) {
+    char text[160];
+    std::snprintf(text, sizeof text,
+                  "matmul size %dx%dx%d must be divisible by CTA %dx%d and BK %d", m, n, k, t.bm,
+                  t.bn, t.bk);
+    return fail(OXGPU_E_SHAPE, text);
+  }
+  const VariantShape shape = variant_shape(e->variant);
+  if (m % shape.tile_m)
+    return fail(OXGPU_E_SHAPE, "this entry is served by a 128-row tcgen05 tile: M must be a multiple of 128");
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  GemmParams p;
+  std::memset(&p, 0, sizeof p);
+  p.a_map_ptr = (const void *)(uintptr_t)a_tmap;
+  p.b_map_ptr = (const void *)(uintptr_t)b_tmap;
+  p.a_box_rows = t.bm;
+  p.b_box_rows = t.bn;
+  // C's row stride is (n / bn) * bn = n (examples/kernels/gemm.ml:61-66).
+  if ((st = encode_2d(&p.map_c, (const void *)(uintptr_t)c, 4, (uint64_t)n, (uint64_t)m,
+                      (uint64_t)n * 4, 32, 32)))
+    return st;
+  LaunchPlan plan{e->element_bytes == 2 ? 0 : 1, e->variant, t.stages, 16, 1, 0, 0};
+  return launch_umma(*dev, plan, p, m, n, k, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_tf32(const float *a, const float *bt, float *c, int m, int n, int k, int64_t lda,
+                         int64_t ldb, int64_t ldc, unsigned flags, void *stream) {
+  if ((flags & 0xffu) == VARIANT_SPLITK)
+    return fail(OXGPU_E_INVALID_ARG, "split-K needs a workspace: use the _ws entry point");
+  return gemm_buffers(1, a, bt, c, m, n, k, lda, ldb, ldc, flags, nullptr, 0, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_bf16(const uint16_t *a, const uint16_t *bt, float *c, int m, int n, int k,
+                         int64_t lda, int64_t ldb, int64_t ldc, unsigned flags, void *stream) {
+  if ((flags & 0xffu) == VARIANT_SPLITK)
+    return fail(OXGPU_E_INVALID_ARG, "split-K needs a workspace: use the _ws entry point");
+  return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, nullptr, 0, (cudaStream_t)stream);
+}
+
+size_t oxgpu_b200_splitk_workspace_bytes(int m, int n, int splits) {
+  if (m <= 0 || n <= 0) return 0;
+  if (splits <= 0) splits = 16;
+  const size_t m_pad = (size_t)((m + 127) / 128) * 128;
+  return (size_t)splits * m_pad * (size_t)n * sizeof(float);
+}
+
+int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, float *c, int m, int n, int k,
+                            int64_t lda, int64_t ldb, int64_t ldc, unsigned flags, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+  return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, workspace, workspace_bytes,
+                      (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_exact(const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
+                          int64_t ldb, int64_t ldc, int input_mode, void *stream) {
+  if (!a || !bt || !c) return fail(OXGPU_E_INVALID_ARG, "null operand pointer");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(OXGPU_E_INVALID_ARG, "M, N and K must be positive");
+  if (lda < k || ldb < k || ldc < n)
+    return fail(OXGPU_E_INVALID_ARG, "leading dimension smaller than the row length");
+  if (input_mode < 0 || input_mode > 2) return fail(OXGPU_E_INVALID_ARG, "input_mode must be 0, 1 or 2");
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  dim3 grid((n + kSimtTile - 1) / kSimtTile, (m + kSimtTile - 1) / kSimtTile, 1);
+  if (grid.y > 65535) return fail(OXGPU_E_TOO_LARGE, "M too large for the exact kernel's grid");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (input_mode == 0)
+    simt_gemm_exact_kernel<0><<<grid, kSimtThreads, 0, s>>>(a, bt, c, m, n, k, lda, ldb, ldc);
+  else if (input_mode == 1)
+    simt_gemm_exact_kernel<1><<<grid, kSimtThreads, 0, s>>>(a, bt, c, m, n, k, lda, ldb, ldc);
+  else
+    simt_gemm_exact_kernel<2><<<grid, kSimtThreads, 0, s>>>(a, bt, c, m, n, k, lda, ldb, ldc);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_bytes, void *stream) {
+  if (!b || !bt) return fail(OXGPU_E_INVALID_ARG, "null pointer");
+  if (k <= 0 || n <= 0) return fail(OXGPU_E_INVALID_ARG, "K and N must be positive");
+  if (element_bytes != 2 && element_bytes != 4)
+    return fail(OXGPU_E_INVALID_ARG, "element_bytes must be 2 or 4");
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  dim3 grid((n + 31) / 32, (k + 31) / 32, 1), block(32, 8, 1);
+  if (grid.y > 65535) return fail(OXGPU_E_TOO_LARGE, "K too large for the transpose grid");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (element_bytes == 2)
+    transpose_kernel<uint16_t><<<grid, block, 0, s>>>((const uint16_t *)b, (uint16_t *)bt, k, n);
+  else
+    transpose_kernel<float><<<grid, block, 0, s>>>((const float *)b, (float *)bt, k, n);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *stream) {
+  if (!src || !dst) return fail(OXGPU_E_INVALID_ARG, "null pointer");
+  if (count == 0) return OXGPU_OK;
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  size_t blocks = (count + 255) / 256;
+  if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
+  f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(src, dst, count);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_gemm_bf16_host(const uint16_t *a_host, const uint16_t *bt_host, float *c_host, int m,
+                              int n, int k, unsigned flags) {
+  return gemm_host(0, a_host, bt_host, c_host, m, n, k, flags);
+}
+
+int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *c_host, int m, int n,
+                              int k, unsigned flags) {
+  return gemm_host(1, a_host, bt_host, c_host, m, n, k, flags);
+}
+
+int oxgpu_b200_release_staging(void) {
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  std::lock_guard<std::mutex> lock(g_staging_mutex);
+  Staging &s = dev->staging;
+  OX_CUDA(cudaDeviceSynchronize());
+  if (s.a) OX_CUDA(cudaFree(s.a));
+  if (s.bt) OX_CUDA(cudaFree(s.bt));
+  if (s.c) OX_CUDA(cudaFree(s.c));
+  s.a = s.bt = s.c = nullptr;
+  s.a_bytes = s.bt_bytes = s.c_bytes = 0;
+  return OXGPU_OK;
+}
+
+static int fill(int dist, void *dst, size_t count, int element_bytes, uint32_t seed, float scale,
+                uint64_t offset, void *stream) {
+  if (!dst) return fail(OXGPU_E_INVALID_ARG, "null pointer");
+  if (element_bytes != 2 && element_bytes != 4)
+    return fail(OXGPU_E_INVALID_ARG, "element_bytes must be 2 or 4");
+  if (count == 0) return OXGPU_OK;
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  size_t blocks = (count + 255) / 256;
+  if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned g = (unsigned)blocks;
+  if (dist == 0 && element_bytes == 4) synth_fill_kernel<0, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
+  else if (dist == 0) synth_fill_kernel<0, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
+  else if (element_bytes == 4) synth_fill_kernel<1, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
+  else synth_fill_kernel<1, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_fill_uniform(void *dst, size_t count, int element_bytes, uint32_t seed,
+                            uint64_t index_offset, void *stream) {
+  return fill(0, dst, count, element_bytes, seed, 1.0f, index_offset, stream);
+}
+
+int oxgpu_b200_fill_normal(void *dst, size_t count, int element_bytes, uint32_t seed, float std_dev,
+                           uint64_t index_offset, void *stream) {
+  return fill(1, dst, count, element_bytes, seed, std_dev, index_offset, stream);
+}
+
+int oxgpu_b200_device_status(uint32_t words[8]) {
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  OX_CUDA(cudaDeviceSynchronize());
+  uint32_t host[8];
+  OX_CUDA(cudaMemcpyFromSymbol(host, g_device_status, sizeof host));
+  if (words) std::memcpy(words, host, sizeof host);
+  if (host[0] != 0) {
+    uint32_t zero[8] = {};
+    OX_CUDA(cudaMemcpyToSymbol(g_device_status, zero, sizeof zero));
+    char text[160];
+    std::snprintf(text, sizeof text,
+                  "device wait timed out: kind %u, block %u, detail %u, parity %u", host[0], host[1],
+                  host[2], host[3]);
+    return fail(OXGPU_E_DEVICE_TIMEOUT, text);
+  }
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_selftest_bounded_wait(uint64_t budget_ns) {
+  int dev_index, st;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  if (budget_ns == 0 || budget_ns > 1000000000ull)
+    return fail(OXGPU_E_INVALID_ARG, "self-test budget must be in (0, 1 s]");
+  bounded_wait_selftest_kernel<<<1, 32>>>((unsigned long long)budget_ns);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return oxgpu_b200_device_status(nullptr);
+}
+
+uint64_t oxgpu_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char *oxgpu_b200_build_info(void) {
+  return "oxgpu_b200: sm_100a; tcgen05 UMMA bf16+tf32; variants 1cta_128x256 1cta_128x128 "
+         "1cta_256x128 2cta_256x256 2cta_256x128 splitk; cudart " OXGPU_STRINGIFY(CUDART_VERSION);
+}
+
+}  // extern "C"

@@ -1,0 +1,440 @@
+// The dense GEMM hot path on sm_100a: C[M,N] f32 = A[M,K] * B^T[N,K]^T with
+// bf16 or TF32 inputs.
+//
+// What it replaces: the reference's Hopper schedule hopper_gemm /
+// hopper_gemm_bf16 (examples/kernels/gemm.ml:47-163, gemm_bf16.ml:33-128),
+// i.e. a TMA producer filling a ring of 128-byte-swizzled K-major stages
+// guarded by full/empty mbarriers, warpgroup WGMMA consumers, grouped CTA
+// order and a vector-store epilogue.  WGMMA does not exist on Blackwell, so
+// the schedule is rebuilt around tcgen05:
+//
+//   warp 0      TMA producer      one lane issues cp.async.bulk.tensor loads
+//   warp 1      UMMA issuer       one lane issues tcgen05.mma; the warp owns the
+//                                 TMEM allocation
+//   warps 2-5   epilogue          tcgen05.ld TMEM -> registers -> swizzled
+//                                 shared staging -> TMA store to C
+//
+// The kernel is persistent: each CTA (or CTA pair) walks tiles
+// first, first+stride, ... in the grouped order, and keeps two accumulators in
+// TMEM so the epilogue of tile i overlaps the main loop of tile i+1.  In the
+// CTA-pair variants (cta_group::2) each CTA stages its own 128 rows of A and
+// its own half of the B^T rows, the leader CTA issues UMMAs that read both
+// CTAs' shared memory, and no load is multicast.
+//
+// Every wait is bounded: when a wait outlives its budget the waiter records
+// where it gave up in the device status block, raises the CTA's abort flag and
+// all roles leave through the common teardown (pending loads/stores drained,
+// TMEM released).  The reference's waits spin forever
+// (lib/backend/ptx.ml:174-181).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.hpp"
+#include "ptx.cuh"
+
+namespace oxgpu {
+
+// Device status block: words[0] = code (0 = healthy), [1] = blockIdx.x,
+// [2] = role-specific detail (stage / tile), [3] = parity, [4] = barrier kind.
+__device__ uint32_t g_device_status[8];
+
+enum WaitKind : uint32_t {
+  WAIT_EMPTY = 1,       // producer waiting for a free ring slot
+  WAIT_FULL = 2,        // issuer waiting for operand bytes
+  WAIT_TMEM_EMPTY = 3,  // issuer waiting for the epilogue to drain an accumulator
+  WAIT_TMEM_FULL = 4,   // epilogue waiting for an accumulator
+  WAIT_DRAIN = 5,       // teardown waiting for in-flight work
+  WAIT_SELFTEST = 6,    // the bounded-wait self test
+};
+
+struct GemmParams {
+  // Tensor maps passed by value (buffer entry points).  a_map_ptr / b_map_ptr,
+  // when non-null, point at caller-owned maps in device memory instead (the
+  // catalog entry points take device pointers to maps, lib/backend/ptx.ml:6-18).
+  CUtensorMap map_a, map_b, map_c;
+  const void *a_map_ptr, *b_map_ptr;
+  int tiles_m, tiles_n, num_k_blocks;
+  int stages;
+  int group_m;
+  int a_box_rows, b_box_rows;  // rows one TMA load brings (the caller's box)
+  int k_block_elems;           // elements per 128-byte K block (64 bf16 / 32 f32)
+  // Split-K: each tile is cut into `splits` K slices of `kb_per_split` blocks;
+  // slice s stores its partial tile `split_row_stride` rows further down the C
+  // map (a [splits * rows, N] workspace).  splits == 1: plain GEMM.
+  int splits, kb_per_split, split_row_stride;
+  unsigned long long wait_budget_ns;
+};
+
+struct WaitCtx {
+  unsigned long long budget_ns;
+  volatile uint32_t *abort_flag;  // shared memory, one per CTA
+};
+
+// Bounded mbarrier wait.  Returns false if the budget ran out (or another
+// role of this CTA already gave up).
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx &ctx,
+                                             uint32_t kind, uint32_t detail) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (ptx::globaltimer_ns() - t0 > ctx.budget_ns) {
+        if (atomicCAS(&g_device_status[0], 0u, kind) == 0u) {
+          g_device_status[1] = blockIdx.x;
+          g_device_status[2] = detail;
+          g_device_status[3] = parity;
+          g_device_status[4] = kind;
+          __threadfence();
+        }
+        *ctx.abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are one
+// 128-byte swizzle span: 8-row atoms 1024 bytes apart (stride byte offset),
+// leading byte offset unused for swizzled K-major, descriptor version 1
+// (sm_100), layout type 2 = 128-byte swizzle.  The reference packs the Hopper
+// form of the same facts (lib/frontend/kernel_frontend.ml:34-51,
+// lib/backend/ptx.ml:182-199); the bit layout differs on Blackwell.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// 32-bit UMMA instruction descriptor: f32 accumulate, both operands K-major.
+template <int KIND>
+__host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
+  uint32_t fmt = KIND == 0 ? 1u /* bf16 */ : 2u /* tf32 */;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(umma_n >> 3) << 17) |
+         ((uint32_t)(umma_m >> 4) << 24);
+}
+
+template <int KIND, int BM_CTA, int BN, int CTA_GROUP>
+__global__ void __launch_bounds__(kThreadsPerCta, 1)
+umma_gemm_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int MMA_M_COUNT = BM_CTA / 128;       // UMMAs along M per K step (1-CTA 256-row tile: 2)
+  constexpr int UMMA_M = 128 * CTA_GROUP;         // rows one instruction produces
+  constexpr int B_ROWS = BN / CTA_GROUP;          // rows of B^T this CTA stages
+  constexpr int ACC_COLS = MMA_M_COUNT * BN;      // TMEM columns of one accumulator set
+  constexpr int TMEM_COLS = 2 * ACC_COLS;         // two sets: epilogue overlaps the next main loop
+  constexpr uint32_t A_BYTES = BM_CTA * 128;
+  constexpr uint32_t B_BYTES = B_ROWS * 128;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t IDESC = instr_desc<KIND>(UMMA_M, BN);
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
+  static_assert(BM_CTA == 128 || (BM_CTA == 256 && CTA_GROUP == 1), "unsupported tile");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int stages = p.stages;
+  const uint32_t staging_base = smem_base + (uint32_t)stages * STAGE_BYTES;
+  const uint32_t bar_base = staging_base + kEpilogueStagingBytes;
+  // barrier region: full[stages], empty[stages], tmem_full[2], tmem_empty[2],
+  // drain, then the TMEM base slot and the abort flag.
+  const uint32_t full_bar = bar_base;
+  const uint32_t empty_bar = bar_base + 8u * kMaxStages;
+  const uint32_t tmem_full_bar = bar_base + 16u * kMaxStages;
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16u;
+  const uint32_t drain_bar = tmem_empty_bar + 16u;
+  const uint32_t tmem_slot = drain_bar + 8u;
+  const uint32_t abort_slot = tmem_slot + 4u;
+  uint8_t *const generic_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t *const tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t *>(generic_base + (tmem_slot - smem_base));
+  volatile uint32_t *const abort_ptr =
+      reinterpret_cast<volatile uint32_t *>(generic_base + (abort_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_ctarank() : 0u;
+  const bool is_leader = cta_rank == 0;
+  const int cluster_id = CTA_GROUP == 2 ? (int)ptx::cluster_id_x() : (int)blockIdx.x;
+  const int num_clusters = CTA_GROUP == 2 ? (int)ptx::num_clusters_x() : (int)gridDim.x;
+
+  const void *map_a = p.a_map_ptr ? p.a_map_ptr : (const void *)&p.map_a;
+  const void *map_b = p.b_map_ptr ? p.b_map_ptr : (const void *)&p.map_b;
+  const void *map_c = (const void *)&p.map_c;
+
+  const WaitCtx wctx{p.wait_budget_ns, abort_ptr};
+  const int total_work = p.tiles_m * p.tiles_n * p.splits;
+
+  // ---- set-up ---------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    *abort_ptr = 0;
+    for (int s = 0; s < stages; s++) {
+      ptx::mbar_init(full_bar + 8u * s, 1);
+      ptx::mbar_init(empty_bar + 8u * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      ptx::mbar_init(tmem_full_bar + 8u * b, 1);
+      // one arrival per epilogue warp of every CTA that feeds this issuer
+      ptx::mbar_init(tmem_empty_bar + 8u * b, 4 * CTA_GROUP);
+    }
+    ptx::mbar_init(drain_bar, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(map_a);
+    ptx::prefetch_tensormap(map_b);
+    ptx::prefetch_tensormap(map_c);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CTA_GROUP>(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish<CTA_GROUP>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    // the peer's barriers must exist before anything arrives on them remotely
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // ---- roles ------------------------------------------------------------------
+  if (warp == 0) {
+    // ===== TMA producer (examples/kernels/gemm.ml:92-98 `prefetch`) =====
+    if (lane == 0) {
+      const uint32_t full_remote0 =
+          CTA_GROUP == 2 ? ptx::map_to_cta(full_bar, 0) : full_bar;  // leader's full[0]
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
+        const int t = w / p.splits, sp = w - t * p.splits;
+        const int kb_begin = sp * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        int tm, tn;
+        grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+        const int a_row0 = tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA;
+        const int b_row0 = tn * BN + (int)cta_rank * B_ROWS;
+        for (int kb = kb_begin; kb < kb_end; kb++) {
+          if (!bounded_wait(empty_bar + 8u * stage, phase ^ 1u, wctx, WAIT_EMPTY, (uint32_t)stage)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + (uint32_t)stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_BYTES;
+          const int kc = kb * p.k_block_elems;
+          if constexpr (CTA_GROUP == 1) {
+            const uint32_t bar = full_bar + 8u * stage;
+            ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
+            for (int r = 0; r < BM_CTA; r += p.a_box_rows)
+              ptx::tma_load_2d(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar);
+            for (int r = 0; r < B_ROWS; r += p.b_box_rows)
+              ptx::tma_load_2d(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar);
+          } else {
+            // Both CTAs credit the leader's barrier; the leader expects the
+            // bytes of the whole pair.
+            if (is_leader) ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * STAGE_BYTES);
+            const uint32_t bar = full_remote0 + 8u * stage;
+            for (int r = 0; r < BM_CTA; r += p.a_box_rows)
+              ptx::tma_load_2d_pair(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar);
+            for (int r = 0; r < B_ROWS; r += p.b_box_rows)
+              ptx::tma_load_2d_pair(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar);
+          }
+          issued++;
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_ptr) {
+        // Abort path: let the loads already issued land before shared memory
+        // is given up.  Slot s was last filled in the phase its full barrier
+        // is (or was) waiting on; both parities are tried with a short budget.
+        const WaitCtx drain{50ull * 1000 * 1000, abort_ptr};
+        if (CTA_GROUP == 1 || is_leader) {
+          long long n = issued < stages ? issued : stages;
+          for (long long i = 0; i < n; i++) {
+            int s = (int)((issued - 1 - i) % stages);
+            uint32_t ph = (uint32_t)(((issued - 1 - i) / stages) & 1);
+            const uint64_t t0 = ptx::globaltimer_ns();
+            while (!ptx::mbar_try_wait(full_bar + 8u * s, ph)) {
+              if (ptx::globaltimer_ns() - t0 > drain.budget_ns) break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== UMMA issuer (examples/kernels/gemm.ml:107-141, the K loop) =====
+    if (lane == 0 && is_leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int w = cluster_id; ok && w < total_work; w += num_clusters, local_tile++) {
+        const int sp = w % p.splits;
+        const int kb_begin = sp * p.kb_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+        if (!bounded_wait(tmem_empty_bar + 8u * acc, acc_phase ^ 1u, wctx, WAIT_TMEM_EMPTY,
+                          (uint32_t)w)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+        for (int kb = kb_begin; kb < kb_end; kb++) {
+          if (!bounded_wait(full_bar + 8u * stage, phase, wctx, WAIT_FULL, (uint32_t)stage)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + (uint32_t)stage * STAGE_BYTES;
+          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int ki = 0; ki < 4; ki++) {
+            // 32 bytes of K per instruction (16 bf16 / 8 tf32): advance the
+            // start address inside the swizzle span, as the reference does with
+            // its `+8*ki` / `+16*ki` element offsets (gemm.ml:121-125).
+            const uint64_t koff = (uint64_t)(ki * 2);
+#pragma unroll
+            for (int mi = 0; mi < MMA_M_COUNT; mi++) {
+              const uint64_t a_row_off = (uint64_t)((mi * 128 * 128) >> 4);
+              ptx::umma<KIND, CTA_GROUP>(d_tmem + (uint32_t)(mi * BN), a_desc + koff + a_row_off,
+                                         b_desc + koff, IDESC, (kb > kb_begin || ki > 0) ? 1u : 0u);
+            }
+          }
+          // frees the ring slot once these UMMAs have read it
+          if constexpr (CTA_GROUP == 1) ptx::umma_commit(empty_bar + 8u * stage);
+          else ptx::umma_commit_pair(empty_bar + 8u * stage, 3);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        // wakes the epilogue of every CTA holding rows of this accumulator
+        if constexpr (CTA_GROUP == 1) ptx::umma_commit(tmem_full_bar + 8u * acc);
+        else ptx::umma_commit_pair(tmem_full_bar + 8u * acc, 3);
+      }
+      if (!ok || *abort_ptr) {
+        // let every UMMA in flight retire before TMEM is released
+        ptx::umma_commit(drain_bar);
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (!ptx::mbar_try_wait(drain_bar, 0)) {
+          if (ptx::globaltimer_ns() - t0 > 50ull * 1000 * 1000) break;
+        }
+      }
+    }
+  } else {
+    // ===== epilogue (examples/kernels/gemm.ml:143-161) =====
+    const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    const int ew = warp - 2;    // staging slot
+    const uint32_t stage_buf0 = staging_base + (uint32_t)ew * 8192u;
+    const uint32_t tmem_empty_remote =
+        CTA_GROUP == 2 ? ptx::map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
+    int local_tile = 0;
+    uint32_t store_count = 0;
+    bool ok = true;
+    for (int w = cluster_id; ok && w < total_work; w += num_clusters, local_tile++) {
+      const int t = w / p.splits, sp = w - t * p.splits;
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+      int tm, tn;
+      grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+      const int c_row0 = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) +
+                         (int)cta_rank * BM_CTA + quad * 32;
+      const int c_col0 = tn * BN;
+      if (!bounded_wait(tmem_full_bar + 8u * acc, acc_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+#pragma unroll 1
+      for (int mi = 0; mi < MMA_M_COUNT; mi++) {
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 32; ch++) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(t_lane + (uint32_t)(mi * BN + ch * 32), v);
+          ptx::tmem_ld_wait();
+          if (mi == MMA_M_COUNT - 1 && ch == BN / 32 - 1) {
+            // the accumulator is now in registers everywhere in this warp:
+            // hand it back to the issuer before finishing the stores
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tmem_empty_bar + 8u * acc);
+              else ptx::mbar_arrive_cluster(tmem_empty_remote + 8u * acc);
+            }
+          }
+          const uint32_t buf = stage_buf0 + (store_count & 1u) * 4096u;
+          // the store that last read this buffer must be done reading it
+          if (lane == 0) ptx::tma_store_wait_read<1>();
+          __syncwarp();
+          // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
+          // (row % 8) as the 128-byte-swizzle store map expects
+          const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                              v[4 * j + 2], v[4 * j + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d(map_c, c_col0 + ch * 32, c_row0 + mi * 128, buf);
+            ptx::tma_store_commit();
+          }
+          store_count++;
+        }
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ---- teardown -----------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) {
+    // the leader's UMMAs read the peer's shared memory and arrive on its
+    // barriers: neither CTA may retire before both are done
+    __syncwarp();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<CTA_GROUP>(tmem_base, TMEM_COLS);
+  }
+}
+
+// The bounded-wait self test: one CTA waits on a barrier nothing arrives on.
+// The wait must give up after `budget_ns`, record WAIT_SELFTEST in the status
+// block and return normally.
+__global__ void bounded_wait_selftest_kernel(unsigned long long budget_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_mbar_init();
+    WaitCtx ctx{budget_ns, &abort_flag};
+    bounded_wait(ptx::smem_u32(&bar), 0, ctx, WAIT_SELFTEST, 0);
+  }
+}
+
+}  // namespace oxgpu

@@ -1,0 +1,231 @@
+"""Host launcher above the C ABI, mirroring the reference's two launchers:
+the C harness test/hardware/run_gemm_h100.cu (encode_tiled_2d 46-72, launch
+164-186) and bench/bench.py (encode_tensor_map_2d 126-147,
+alloc_device_tensor_map 150-156, launch_mm 281-292).
+
+torch is used for device memory and streams only; every GEMM below is a call
+into liboxgpu_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import catalog
+from ._lib import check, lib
+
+VARIANT_AUTO, V_1CTA_128x256, V_1CTA_128x128, V_1CTA_256x128, V_2CTA_256x256, V_2CTA_256x128, V_SPLITK = range(7)
+VARIANT_NAMES = {
+    "auto": VARIANT_AUTO, "1cta_128x256": V_1CTA_128x256, "1cta_128x128": V_1CTA_128x128,
+    "1cta_256x128": V_1CTA_256x128, "2cta_256x256": V_2CTA_256x256, "2cta_256x128": V_2CTA_256x128,
+    "splitk": V_SPLITK,
+}
+ELEMENT_BYTES = {"f32": 4, "bf16": 2}
+INPUT_NONE, INPUT_TF32, INPUT_BF16 = 0, 1, 2
+
+
+def make_flags(variant: int | str = VARIANT_AUTO, stages: int = 0, group_m: int = 0, splits: int = 0) -> int:
+    if isinstance(variant, str):
+        variant = VARIANT_NAMES[variant]
+    return (variant & 0xFF) | ((stages & 0xF) << 8) | ((group_m & 0xFF) << 12) | ((splits & 0xFF) << 20)
+
+
+def _stream(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return int(s.cuda_stream)
+
+
+class TensorMap(ctypes.Structure):
+    """A 128-byte CUtensorMap in host memory (64-byte aligned)."""
+    _fields_ = [("opaque", ctypes.c_uint64 * 16)]
+    _align_ = 64
+
+
+def encode_tensor_map_2d(device_ptr: int, dim0: int, dim1: int, stride1_bytes: int, box0: int,
+                         box1: int, element: str = "f32") -> ctypes.Array:
+    """bench/bench.py:126-147 / run_gemm_h100.cu:46-72: 2-D tiled, 128-byte
+    swizzle, L2 promotion 128 B, zero fill."""
+    raw = (ctypes.c_uint8 * 192)()
+    base = ctypes.addressof(raw)
+    off = (-base) % 64
+    check(lib().oxgpu_b200_encode_tmap_2d(ctypes.c_void_p(base + off), ctypes.c_void_p(device_ptr),
+                                          ELEMENT_BYTES[element], dim0, dim1, stride1_bytes, box0,
+                                          box1))
+    out = (ctypes.c_uint8 * 128)()
+    ctypes.memmove(out, base + off, 128)
+    return out
+
+
+def alloc_device_tensor_map(host_map) -> torch.Tensor:
+    """bench/bench.py:150-156: copy a host CUtensorMap into device memory."""
+    cpu = torch.empty(128, dtype=torch.uint8)
+    ctypes.memmove(cpu.data_ptr(), host_map, 128)
+    return cpu.cuda()
+
+
+def launch_catalog(name: str, d_a_map: torch.Tensor, d_b_map: torch.Tensor, c: torch.Tensor, m: int,
+                   n: int, k: int, stream=None) -> None:
+    """Launch a catalog entry point with reference-style arguments (device
+    pointers to the A and B^T maps, C, m, n, k): run_gemm_h100.cu:183-185."""
+    check(lib().oxgpu_b200_gemm_tmap(name.encode(), d_a_map.data_ptr(), d_b_map.data_ptr(),
+                                     c.data_ptr(), m, n, k, ctypes.c_void_p(_stream(stream))))
+
+
+def run_catalog_entry(name: str, a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None):
+    """Everything the reference's harness does around one launch: encode the
+    maps with the entry's boxes, put them in device memory, launch."""
+    tile, ebytes = catalog.kernel_tile(name)
+    element = "bf16" if ebytes == 2 else "f32"
+    m, k = a.shape
+    n = bt.shape[0]
+    if c is None:
+        c = torch.empty(m, n, device=a.device, dtype=torch.float32)
+    a_map = encode_tensor_map_2d(a.data_ptr(), k, m, k * ebytes, tile.bk, tile.bm, element)
+    b_map = encode_tensor_map_2d(bt.data_ptr(), k, n, k * ebytes, tile.bk, tile.bn, element)
+    da, db = alloc_device_tensor_map(a_map), alloc_device_tensor_map(b_map)
+    launch_catalog(name, da, db, c, m, n, k)
+    c._oxgpu_keepalive = (da, db)
+    return c
+
+
+def _check_operands(a: torch.Tensor, bt: torch.Tensor, dtype) -> tuple[int, int, int]:
+    if not (a.is_cuda and bt.is_cuda):
+        raise ValueError("operands must be CUDA tensors")
+    if a.dtype != dtype or bt.dtype != dtype:
+        raise ValueError(f"operands must be {dtype}")
+    if a.dim() != 2 or bt.dim() != 2 or a.shape[1] != bt.shape[1]:
+        raise ValueError("expected A[M,K] and B^T[N,K]")
+    if a.stride(1) != 1 or bt.stride(1) != 1:
+        raise ValueError("operands must be K-contiguous")
+    return a.shape[0], bt.shape[0], a.shape[1]
+
+
+def _out(c, m, n, device):
+    if c is None:
+        c = torch.empty(m, n, device=device, dtype=torch.float32)
+    if c.dtype != torch.float32 or c.stride(1) != 1 or tuple(c.shape) != (m, n):
+        raise ValueError("C must be f32 [M,N] with unit column stride")
+    return c
+
+
+def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
+              workspace: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """C = A * B with bf16 A[M,K], B^T[N,K]; f32 out (gemm_bf16.ml:33-128)."""
+    m, n, k = _check_operands(a, bt, torch.bfloat16)
+    c = _out(c, m, n, a.device)
+    s = ctypes.c_void_p(_stream(stream))
+    if (flags & 0xFF) == V_SPLITK:
+        if workspace is None:
+            need = lib().oxgpu_b200_splitk_workspace_bytes(m, n, (flags >> 20) & 0xFF)
+            workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+        check(lib().oxgpu_b200_gemm_bf16_ws(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k,
+                                            a.stride(0), bt.stride(0), c.stride(0), flags,
+                                            workspace.data_ptr(), workspace.numel() * workspace.element_size(), s))
+        c._oxgpu_keepalive = workspace
+    else:
+        check(lib().oxgpu_b200_gemm_bf16(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k,
+                                         a.stride(0), bt.stride(0), c.stride(0), flags, s))
+    return c
+
+
+def gemm_tf32(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
+              stream=None) -> torch.Tensor:
+    """C = A * B with f32 A[M,K], B^T[N,K] rounded to TF32 by the matrix unit
+    (gemm.ml:47-163)."""
+    m, n, k = _check_operands(a, bt, torch.float32)
+    c = _out(c, m, n, a.device)
+    check(lib().oxgpu_b200_gemm_tf32(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0),
+                                     bt.stride(0), c.stride(0), flags, ctypes.c_void_p(_stream(stream))))
+    return c
+
+
+def gemm_exact(a: torch.Tensor, bt: torch.Tensor, input_mode: int, c: torch.Tensor | None = None,
+               stream=None) -> torch.Tensor:
+    """Bit-exact device restatement of the host reference loop
+    (run_gemm_h100.cu:150-162) -- see oxgpu_b200_gemm_exact."""
+    dtype = torch.bfloat16 if input_mode == INPUT_BF16 else torch.float32
+    m, n, k = _check_operands(a, bt, dtype)
+    c = _out(c, m, n, a.device)
+    check(lib().oxgpu_b200_gemm_exact(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0),
+                                      bt.stride(0), c.stride(0), input_mode,
+                                      ctypes.c_void_p(_stream(stream))))
+    return c
+
+
+def transpose(b: torch.Tensor, stream=None) -> torch.Tensor:
+    """B[K,N] -> B^T[N,K] on the device (run_gemm_h100.cu:142-148, bench.py:268)."""
+    if not b.is_cuda or b.dim() != 2 or not b.is_contiguous() or b.element_size() not in (2, 4):
+        raise ValueError("expected a contiguous 2-D CUDA tensor of 2- or 4-byte elements")
+    k, n = b.shape
+    bt = torch.empty(n, k, device=b.device, dtype=b.dtype)
+    check(lib().oxgpu_b200_transpose(b.data_ptr(), bt.data_ptr(), k, n, b.element_size(),
+                                     ctypes.c_void_p(_stream(stream))))
+    return bt
+
+
+def f32_to_bf16(x: torch.Tensor, stream=None) -> torch.Tensor:
+    """Round-to-nearest-even f32 -> bf16 (run_gemm_h100.cu:26-30)."""
+    if not x.is_cuda or x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("expected a contiguous f32 CUDA tensor")
+    out = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16)
+    check(lib().oxgpu_b200_f32_to_bf16(x.data_ptr(), out.data_ptr(), x.numel(),
+                                       ctypes.c_void_p(_stream(stream))))
+    return out
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, element: str = "f32", flags: int = 0) -> torch.Tensor:
+    """A[M,K] @ B[K,N] the way the reference's bench drives its kernel
+    (bench.py:255-271): convert to the input width, re-lay B K-major, launch."""
+    if element == "bf16":
+        a16 = a if a.dtype == torch.bfloat16 else f32_to_bf16(a.contiguous())
+        b16 = b if b.dtype == torch.bfloat16 else f32_to_bf16(b.contiguous())
+        return gemm_bf16(a16, transpose(b16.contiguous()), flags=flags)
+    return gemm_tf32(a.contiguous(), transpose(b.contiguous()), flags=flags)
+
+
+def gemm_bf16_host(a_host: torch.Tensor, bt_host: torch.Tensor, c_host: torch.Tensor, flags: int = 0) -> torch.Tensor:
+    """Host-buffer entry point: operands and result in (pinned) host memory."""
+    if a_host.is_cuda or bt_host.is_cuda or c_host.is_cuda:
+        raise ValueError("host entry point takes CPU tensors")
+    m, k = a_host.shape
+    n = bt_host.shape[0]
+    check(lib().oxgpu_b200_gemm_bf16_host(a_host.data_ptr(), bt_host.data_ptr(), c_host.data_ptr(),
+                                          m, n, k, flags))
+    return c_host
+
+
+def gemm_tf32_host(a_host: torch.Tensor, bt_host: torch.Tensor, c_host: torch.Tensor, flags: int = 0) -> torch.Tensor:
+    if a_host.is_cuda or bt_host.is_cuda or c_host.is_cuda:
+        raise ValueError("host entry point takes CPU tensors")
+    m, k = a_host.shape
+    n = bt_host.shape[0]
+    check(lib().oxgpu_b200_gemm_tf32_host(a_host.data_ptr(), bt_host.data_ptr(), c_host.data_ptr(),
+                                          m, n, k, flags))
+    return c_host
+
+
+def fill_uniform(t: torch.Tensor, seed: int, offset: int = 0, stream=None) -> torch.Tensor:
+    """uniform[-1,1) from the counter-based generator, in place."""
+    check(lib().oxgpu_b200_fill_uniform(t.data_ptr(), t.numel(), t.element_size(), seed, offset,
+                                        ctypes.c_void_p(_stream(stream))))
+    return t
+
+
+def fill_normal(t: torch.Tensor, seed: int, std: float = 1.0, offset: int = 0, stream=None) -> torch.Tensor:
+    """normal(0, std) from the counter-based generator, in place (f32 or bf16)."""
+    check(lib().oxgpu_b200_fill_normal(t.data_ptr(), t.numel(), t.element_size(), seed, std, offset,
+                                       ctypes.c_void_p(_stream(stream))))
+    return t
+
+
+def device_status() -> list[int]:
+    """Synchronise and read the device status block; raises OxgpuError
+    (status -7) if a bounded device wait timed out."""
+    words = (ctypes.c_uint32 * 8)()
+    check(lib().oxgpu_b200_device_status(words))
+    return list(words)
+
+
+def launch_count() -> int:
+    return int(lib().oxgpu_b200_launch_count())

@@ -1,0 +1,144 @@
+"""Catalog parity with the reference's Gemm_catalog (test/gemm_catalog.ml) and
+the answers its emitter CLI is pinned to (test/check_oxcaml_signature.sh:234-251).
+Host logic only: no GPU."""
+import pytest
+
+from oxcamlgpu_b200 import catalog as cat
+from oxcamlgpu_b200.catalog import TileConfig
+
+
+def test_print_choose_answers_pinned_by_the_reference(oxlib):
+    # test/check_oxcaml_signature.sh:234-251
+    assert cat.print_choose(4096, 4096, 4096) == "gemm_fast 128 256 32 288"
+    assert cat.print_choose(8192, 8192, 8192) == "gemm_fast 128 256 32 288"
+    assert cat.print_config("bm=64,bn=256,bk=32,stages=2,producers=32,threads=160") == \
+        "gemm_bm64_bn256_s2 64 256 32 160"
+
+
+def test_choose_config_branches(oxlib):
+    # test/gemm_catalog.ml:131-136
+    assert cat.choose_config(8192, 4096, 64) == TileConfig(256, 128, 32, 3, 32)       # m >= 2n
+    assert cat.choose_config(8192, 4097, 64) == TileConfig(128, 256, 32, 4, 32)
+    assert cat.choose_config(256, 256, 256) == TileConfig(64, 256, 32, 3, 32)         # small, square-ish
+    assert cat.choose_config(1024, 1024, 1) == TileConfig(64, 256, 32, 3, 32)
+    assert cat.choose_config(1024, 512, 1) == TileConfig(256, 128, 32, 3, 32)         # m >= 2n wins first
+    assert cat.choose_config(512, 1024, 1) == TileConfig(128, 256, 32, 4, 32)         # n >= 2m
+    assert cat.choose_config(1025, 1024, 1) == TileConfig(128, 256, 32, 4, 32)
+    assert cat.choose_config() == TileConfig(128, 256, 32, 4, 32)                     # defaults 4096
+    # the workload shapes: rectangular projections, skinny M, sharded
+    assert cat.kernel_binding(cat.choose_config(8192, 28672, 8192)) == "gemm_fast"
+    assert cat.kernel_binding(cat.choose_config(128, 8192, 8192)) == "gemm_fast"
+    assert cat.kernel_binding(cat.choose_config(32768, 8192, 8192)) == "gemm_bm256_bn128_s3"
+
+
+def test_tile_catalog_and_bindings(oxlib):
+    tiles = cat.tile_catalog()
+    assert tiles == [TileConfig(128, 256, 32, 4, 32), TileConfig(128, 256, 32, 3, 32),
+                     TileConfig(128, 256, 32, 2, 32), TileConfig(128, 128, 32, 3, 32),
+                     TileConfig(128, 128, 32, 2, 32), TileConfig(64, 256, 32, 3, 32),
+                     TileConfig(256, 128, 32, 3, 32)]
+    assert cat.hopper_f32() == tiles[0]
+    assert [cat.kernel_binding(t) for t in tiles] == [
+        "gemm_fast", "gemm_bm128_bn256_s3", "gemm_bm128_bn256_s2", "gemm_bm128_bn128_s3",
+        "gemm_bm128_bn128_s2", "gemm_bm64_bn256_s3", "gemm_bm256_bn128_s3"]
+    assert cat.kernel_binding(TileConfig(64, 256, 32, 2, 32)) == "gemm_bm64_bn256_s2"
+    assert cat.kernel_binding(TileConfig(256, 128, 32, 2, 32)) == "gemm_bm256_bn128_s2"
+    with pytest.raises(ValueError, match="no OxCaml kernel for bm=128,bn=64,bk=32,stages=3,producers=32,threads=288"):
+        cat.kernel_binding(TileConfig(128, 64, 32, 3, 32))
+    assert cat.list_catalog()[0] == "bm=128,bn=256,bk=32,stages=4,producers=32,threads=288"
+    assert cat.list_catalog()[5] == "bm=64,bn=256,bk=32,stages=3,producers=32,threads=160"
+    assert cat.list_catalog()[6] == "bm=256,bn=128,bk=32,stages=3,producers=32,threads=544"
+
+
+def test_threads(oxlib):
+    # consumers = 128 * (bm / 64), threads = consumers + producers
+    assert cat.threads(TileConfig(128, 256, 32, 4, 32)) == 288
+    assert cat.threads(TileConfig(64, 256, 32, 3, 32)) == 160
+    assert cat.threads(TileConfig(256, 128, 32, 3, 32)) == 544
+    assert cat.consumers(TileConfig(256, 128, 32, 3, 64)) == 512 and cat.warp_groups(TileConfig(192, 8, 32, 2, 32)) == 3
+
+
+@pytest.mark.parametrize("cfg,msg", [
+    (TileConfig(96, 256, 32, 3, 32), "BM must be a positive multiple of 64"),
+    (TileConfig(0, 256, 32, 3, 32), "BM must be a positive multiple of 64"),
+    (TileConfig(128, 260, 32, 3, 32), "BN must be in"),
+    (TileConfig(128, 0, 32, 3, 32), "BN must be in"),
+    (TileConfig(128, 264, 32, 3, 32), "BN must be in"),
+    (TileConfig(128, 256, 64, 3, 32), "BK must be 32"),
+    (TileConfig(128, 256, 16, 3, 32), "BK must be 32"),
+    (TileConfig(128, 256, 32, 1, 32), "pipeline stages must be"),
+    (TileConfig(128, 256, 32, 3, 0), "producers must be a positive multiple"),
+    (TileConfig(128, 256, 32, 3, 48), "producers must be a positive multiple"),
+    (TileConfig(512, 256, 32, 3, 32), "CTA threads"),
+])
+def test_validate_rejections(oxlib, cfg, msg):
+    with pytest.raises(ValueError, match=msg):
+        cat.validate(cfg)
+
+
+def test_validate_accepts(oxlib):
+    for t in cat.tile_catalog():
+        assert cat.validate(t) == t
+    assert cat.validate(TileConfig(448, 8, 32, 2, 128)) == TileConfig(448, 8, 32, 2, 128)  # 1024 threads
+
+
+def test_parse_config(oxlib):
+    assert cat.parse_config("bm=128,bn=256,bk=32,stages=4,producers=32") == TileConfig(128, 256, 32, 4, 32)
+    # stages defaults to 3; unknown keys (legacy tm/tn, threads) ignored; whitespace trimmed
+    assert cat.parse_config(" bm = 128 , bn=128,bk=32, producers=32 ,tm=8,tn=8") == TileConfig(128, 128, 32, 3, 32)
+    assert cat.parse_config(cat.string_of_config(TileConfig(64, 256, 32, 2, 32))) == TileConfig(64, 256, 32, 2, 32)
+    with pytest.raises(ValueError, match="bad config fragment: bm"):
+        cat.parse_config("bm,bn=1")
+    with pytest.raises(ValueError, match="bad config fragment: bm=1=2"):
+        cat.parse_config("bm=1=2")
+    with pytest.raises(ValueError, match="config key bm is not an integer: oops"):
+        cat.parse_config("bm=oops,bn=256,bk=32,producers=32")
+    with pytest.raises(ValueError, match="missing config key: producers"):
+        cat.parse_config("bm=128,bn=256,bk=32")
+    with pytest.raises(ValueError, match="missing config key: bn"):
+        cat.parse_config("bm=128,bk=32,producers=32")
+    with pytest.raises(ValueError, match="BK must be 32"):
+        cat.parse_config("bm=128,bn=256,bk=64,producers=32")
+    with pytest.raises(ValueError, match="bad config fragment: $"):
+        cat.parse_config("")
+
+
+def test_kernel_info_and_tiles(oxlib):
+    for name in cat.ENTRY_NAMES:
+        threads, dyn, total = cat.kernel_info(name)
+        assert threads == 192                       # 6 warps: TMA, UMMA, 4 epilogue
+        assert 118784 <= dyn <= 232448 and total == dyn
+        tile, eb = cat.kernel_tile(name)
+        assert eb == (2 if name == "gemm_bf16_fast" else 4)
+        assert tile.bk * eb == 128                  # one 128-byte swizzle row per K block
+    assert cat.kernel_tile("gemm_fast")[0] == TileConfig(128, 256, 32, 4, 32)
+    assert cat.kernel_tile("gemm_bf16_fast")[0] == TileConfig(128, 256, 64, 4, 32)
+    # deeper rings need more shared memory
+    assert cat.kernel_info("gemm_fast")[1] > cat.kernel_info("gemm_bm128_bn256_s3")[1] > \
+        cat.kernel_info("gemm_bm128_bn256_s2")[1]
+    with pytest.raises(ValueError, match="no kernel named gemm_slow"):
+        cat.kernel_info("gemm_slow")
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,group", [(64, 32, 16), (5, 3, 16), (17, 4, 16), (33, 1, 16),
+                                                   (1, 9, 16), (20, 7, 8), (16, 16, 16), (31, 2, 4)])
+def test_grouped_tile_is_a_bijection(oxlib, tiles_m, tiles_n, group):
+    """tools/exporter/export_prims_index.ml:33-39: every tile exactly once,
+    including a short last group."""
+    seen = set()
+    for pid in range(tiles_m * tiles_n):
+        tm, tn = cat.grouped_tile(pid, group, tiles_m, tiles_n)
+        assert 0 <= tm < tiles_m and 0 <= tn < tiles_n
+        # independent restatement of the formula
+        per_group = group * tiles_n
+        first = (pid // per_group) * group
+        rows = min(tiles_m - first, group)
+        assert (tm, tn) == (first + pid % rows, (pid % per_group) // rows)
+        seen.add((tm, tn))
+    assert len(seen) == tiles_m * tiles_n
+    # a group walks `group` tile-rows before moving along N
+    if tiles_m >= group and tiles_n > 1:
+        assert [cat.grouped_tile(p, group, tiles_m, tiles_n) for p in range(group + 1)] == \
+            [(i, 0) for i in range(group)] + [(0, 1)]
+    with pytest.raises(ValueError):
+        cat.grouped_tile(tiles_m * tiles_n, group, tiles_m, tiles_n)
