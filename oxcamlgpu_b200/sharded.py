@@ -1,0 +1,89 @@
+"""Column-sharded GEMM over several GPUs: one process per GPU.
+
+C[:, n0:n1] = A @ B[:, n0:n1] needs no exchange: with B held K-major as
+B^T[N,K], a column block of B is a contiguous row block of B^T.  Rank r owns
+rows [n0, n1) of B^T, a replica of A, and produces the [M, n1-n0] shard of C.
+The reference has no multi-GPU code; the single-GPU call each rank makes is the
+same C-ABI entry point as everywhere else.
+
+An all-gather of C (NCCL over NVLink when the process group is NCCL) is
+optional and separate from the GEMM: NCCL gathers contiguous chunks, so the
+gathered buffer is block-column-major [world][M][N/world]; blocks_to_row_major
+re-interleaves it into C[M,N] when a row-major replica is wanted.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+COLUMN_ALIGN = 256  # shard widths are multiples of the widest tile
+
+
+def column_partition(n: int, world: int, align: int = COLUMN_ALIGN) -> list[tuple[int, int]]:
+    """Contiguous column ranges [n0, n1) per rank: widths are multiples of
+    `align` except possibly the last non-empty one (the ragged tail), and block
+    counts differ by at most one."""
+    if n <= 0 or world <= 0 or align <= 0:
+        raise ValueError("n, world and align must be positive")
+    blocks = (n + align - 1) // align
+    base, extra = divmod(blocks, world)
+    out, start = [], 0
+    for r in range(world):
+        width_blocks = base + (1 if r < extra else 0)
+        n0 = min(start * align, n)
+        n1 = min((start + width_blocks) * align, n)
+        out.append((n0, n1))
+        start += width_blocks
+    return out
+
+
+def shard_rows_of_bt(bt_full: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rank's rows of B^T[N,K] (= its columns of B); a view, no copy."""
+    n0, n1 = column_partition(bt_full.shape[0], world)[rank]
+    return bt_full[n0:n1]
+
+
+def all_gather_c(c_shard: torch.Tensor, group=None) -> torch.Tensor:
+    """Gather equal-width shards [M, N/world] into [world, M, N/world].  Works on
+    any backend (NCCL on GPUs, gloo on CPU tensors)."""
+    world = dist.get_world_size(group)
+    c_shard = c_shard.contiguous()
+    m, w = c_shard.shape
+    out = torch.empty((world * m, w), dtype=c_shard.dtype, device=c_shard.device)
+    dist.all_gather_into_tensor(out, c_shard, group=group)  # concatenation along dim 0
+    return out.view(world, m, w)
+
+
+def blocks_to_row_major(gathered: torch.Tensor) -> torch.Tensor:
+    """[world, M, W] block-column-major -> row-major C[M, world*W]."""
+    world, m, w = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, world * w).contiguous()
+
+
+class ColumnShardedGemm:
+    """bf16 GEMM with B and C column-sharded across the ranks of a process
+    group and A replicated.  Each rank launches the single-GPU kernel on its
+    shard; nothing crosses NVLink unless gather() is called."""
+
+    def __init__(self, m: int, n: int, k: int, group=None, flags: int = 0):
+        from . import gemm  # needs the CUDA library
+        self._gemm = gemm
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.m, self.n, self.k = m, n, k
+        self.flags = flags
+        self.n0, self.n1 = column_partition(n, self.world)[self.rank]
+        self.width = self.n1 - self.n0
+
+    def run(self, a: torch.Tensor, bt_shard: torch.Tensor, c_shard: torch.Tensor | None = None) -> torch.Tensor:
+        if tuple(bt_shard.shape) != (self.width, self.k) or tuple(a.shape) != (self.m, self.k):
+            raise ValueError("operand shapes do not match this rank's shard")
+        return self._gemm.gemm_bf16(a, bt_shard, c_shard, flags=self.flags)
+
+    def gather(self, c_shard: torch.Tensor, row_major: bool = False) -> torch.Tensor:
+        widths = {hi - lo for lo, hi in column_partition(self.n, self.world)}
+        if len(widths) != 1:
+            raise ValueError("all_gather needs equal shard widths")
+        g = all_gather_c(c_shard, self.group)
+        return blocks_to_row_major(g) if row_major else g

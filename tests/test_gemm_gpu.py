@@ -1,0 +1,430 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Tolerances (inputs are rounded identically on both sides, so only accumulation
+differs):
+  strict   max|C - C_ref| <= 1e-5 * sqrt(K) * max|A| * max|B|.  Asserted for every
+           tensor-core case with K <= 2048 (zero-mean inputs) -- and trivially for
+           the exact path, which is bit-identical.
+  tc       max|C - C_ref| <= 5e-5 * sqrt(K) * max|A| * max|B|: the stated relative
+           tolerance, scaled by sqrt(K), for TF32/bf16 inputs with f32 accumulation
+           in the matrix unit at large K.  The unit's accumulator drops low bits
+           when it aligns addends (one-sided, so the difference to a sequential
+           IEEE sum grows with the number of UMMA steps): measured 1.9e-5*sqrt(K)
+           at TF32 4096^3 with uniform[-1,1) inputs.
+  pattern  the reference's own thresholds, 5e-2 (f32/TF32) and 2e-1 (bf16)
+           (run_gemm_h100.cu:193), plus a relative bound of 2^-16: the pattern
+           inputs are all positive, so both sides carry O(K) one-sided rounding
+           and the zero-mean bound does not apply to them.
+  exact    0 -- the exact kernel repeats the oracle's operation order.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oxcamlgpu_b200 import catalog as cat
+from oxcamlgpu_b200 import gemm, synth
+from oxcamlgpu_b200._lib import OxgpuError
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TC_VARIANTS = ["1cta_128x256", "1cta_128x128", "1cta_256x128", "2cta_256x256", "2cta_256x128"]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device(oxlib):
+    assert torch.cuda.is_available(), "these tests need a GPU"
+    torch.cuda.set_device(0)
+    yield
+    # every test must leave the status block clean: no bounded wait may have expired
+    assert gemm.device_status()[0] == 0
+
+
+def bf16_tensor(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).to(DEV)
+
+
+def rand_bf16(rng, rows, cols, scale=1.0):
+    return oracle.to_bf16((rng.standard_normal((rows, cols)) * scale).astype(np.float32))
+
+
+def strict_tol(k, a_max, b_max):
+    return oracle.tolerance(k, a_max, b_max)
+
+
+def tc_tol(k, a_max, b_max):
+    return 5.0 * oracle.tolerance(k, a_max, b_max)
+
+
+def check_bf16(a_bits, bt_bits, got, rows=None):
+    expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits, rows=rows, threads=oracle.max_threads())
+    g = got.float().cpu().numpy()
+    if rows is not None:
+        g = g[rows]
+    tol = strict_tol(a_bits.shape[1], float(np.abs(oracle.of_bf16(a_bits)).max()),
+                     float(np.abs(oracle.of_bf16(bt_bits)).max()))
+    err = float(np.abs(g - expect).max())
+    assert err <= tol, (err, tol)
+    return err, tol
+
+
+# ---- exact kernel: bit-identical to the oracle -----------------------------------
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (100, 72, 40), (1, 1, 1), (129, 257, 33), (128, 128, 512)])
+@pytest.mark.parametrize("mode", [oracle.MODE_NONE, oracle.MODE_TF32, oracle.MODE_BF16])
+def test_exact_kernel_is_bit_identical(m, n, k, mode):
+    rng = np.random.default_rng(m * 1000 + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    bt = rng.standard_normal((n, k)).astype(np.float32)
+    if mode == oracle.MODE_BF16:
+        a_bits, bt_bits = oracle.to_bf16(a), oracle.to_bf16(bt)
+        got = gemm.gemm_exact(bf16_tensor(a_bits), bf16_tensor(bt_bits), gemm.INPUT_BF16)
+        expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits)
+    else:
+        got = gemm.gemm_exact(torch.from_numpy(a).to(DEV), torch.from_numpy(bt).to(DEV), mode)
+        expect = oracle.gemm_kmajor(a, bt, mode)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), expect.view(np.uint32))
+
+
+def test_config1_f32_256_against_golden(golden_dir):
+    """f32 256^3, uniform[-1,1) seed 0: the exact path reproduces the host loop
+    bit for bit; the TF32 tensor-core path meets the strict bound against the
+    TF32-rounded oracle."""
+    g = np.load(os.path.join(golden_dir, "uniform_seed0_256.npz"))
+    a = torch.empty(256, 256, device=DEV)
+    b = torch.empty(256, 256, device=DEV)
+    gemm.fill_uniform(a, 0, 0)
+    gemm.fill_uniform(b, 0, 256 * 256)
+    a_h = synth.uniform_pm1(0, 256 * 256).reshape(256, 256)
+    b_h = synth.uniform_pm1(0, 256 * 256, offset=256 * 256).reshape(256, 256)
+    assert np.array_equal(a.cpu().numpy(), a_h) and np.array_equal(b.cpu().numpy(), b_h)
+    bt = gemm.transpose(b)
+    assert np.array_equal(bt.cpu().numpy(), b_h.T)
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_NONE).cpu().numpy()
+    assert np.array_equal(exact.view(np.uint32), g["expect_f32"].view(np.uint32))
+    tol = strict_tol(256, 1.0, 1.0)
+    rows = g["rows"]
+    for variant in TC_VARIANTS:
+        c = gemm.gemm_tf32(a, bt, flags=gemm.make_flags(variant)).cpu().numpy()
+        err = np.abs(c[rows] - g["expect_tf32_rows"]).max()
+        assert err <= tol, (variant, err, tol)
+    # through the catalog entry the reference's choose_config picks for 256^3
+    name = cat.kernel_binding(cat.choose_config(256, 256, 256))
+    assert name == "gemm_bm64_bn256_s3"
+    c = gemm.run_catalog_entry(name, a, bt).cpu().numpy()
+    assert np.abs(c[rows] - g["expect_tf32_rows"]).max() <= tol
+    full = oracle.gemm_kmajor(a_h, np.ascontiguousarray(b_h.T), oracle.MODE_TF32, threads=oracle.max_threads())
+    assert np.abs(c - full).max() <= tol
+
+
+# ---- the harness's pattern cases through the catalog entry points -----------------
+@pytest.mark.parametrize("name,fixture,k,narrow", [("gemm_fast", "pattern_f32_k512", 512, False),
+                                                  ("gemm_bf16_fast", "pattern_bf16_k1024", 1024, True)])
+def test_pattern_case_through_catalog_entry(golden_dir, name, fixture, k, narrow):
+    """run_gemm_h100.cu:113-118: M=N=256, K = 16 K-blocks so the ring wraps and
+    the barrier parity flips both ways."""
+    expect = np.load(os.path.join(golden_dir, fixture + ".npz"))["expect"]
+    a, b = oracle.pattern_inputs(256, 256, k)
+    a_dev, bt_dev = oracle.prepare_operands(a, b, narrow)
+    if narrow:
+        ta, tb = bf16_tensor(a_dev), bf16_tensor(bt_dev)
+    else:
+        ta, tb = torch.from_numpy(a_dev).to(DEV), torch.from_numpy(bt_dev).to(DEV)
+    c = torch.full((256, 256), float("nan"), device=DEV)
+    gemm.run_catalog_entry(name, ta, tb, c)
+    got = c.cpu().numpy()
+    first, worst = oracle.compare_abs(got, expect, oracle.REFERENCE_ABS_TOL["bf16" if narrow else "f32"])
+    assert first == -1, (first, worst)
+    rel = np.abs(got - expect) / np.abs(expect)
+    assert rel.max() <= 2.0 ** -16, rel.max()
+
+
+@pytest.mark.parametrize("name", cat.ENTRY_NAMES)
+def test_every_catalog_entry(name):
+    tile, eb = cat.kernel_tile(name)
+    rng = np.random.default_rng(abs(hash(name)) % 1000)
+    m, n, k = 512, 512, 5 * tile.bk
+    if eb == 2:
+        a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+        c = gemm.run_catalog_entry(name, bf16_tensor(a_bits), bf16_tensor(bt_bits))
+        check_bf16(a_bits, bt_bits, c)
+    else:
+        a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+        bt = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+        c = gemm.run_catalog_entry(name, torch.from_numpy(a).to(DEV), torch.from_numpy(bt).to(DEV))
+        expect = oracle.gemm_kmajor(a, bt, oracle.MODE_TF32, threads=oracle.max_threads())
+        assert np.abs(c.cpu().numpy() - expect).max() <= strict_tol(k, 1.0, 1.0)
+
+
+def test_catalog_entry_rejects_bad_sizes():
+    a = torch.zeros(256, 512, device=DEV)
+    with pytest.raises(OxgpuError) as e:
+        gemm.run_catalog_entry("gemm_fast", a[:200].contiguous(), a)
+    assert e.value.status == -4
+
+
+# ---- one-hot probes: descriptor / swizzle / TMEM-map errors show up as permutations
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+def test_one_hot_probes_bf16(variant):
+    rng = np.random.default_rng(11)
+    m = n = 512
+    k = 192
+    bt_bits = rand_bf16(rng, n, k)
+    bt = bf16_tensor(bt_bits)
+    bt_f = oracle.of_bf16(bt_bits)
+    picks = [(0, 0), (5, 17), (127, 63), (128, 64), (300, 191), (511, 100), (200, 15), (77, 130)]
+    a = np.zeros((m, k), np.float32)
+    for r, kk in picks:
+        a[r, kk] = 1.0
+    c = gemm.gemm_bf16(bf16_tensor(oracle.to_bf16(a)), bt, flags=gemm.make_flags(variant)).cpu().numpy()
+    expect = np.zeros((m, n), np.float32)
+    for r, kk in picks:
+        expect[r] = bt_f[:, kk]
+    assert np.array_equal(c, expect)          # exact: one product per output
+    # and the other way round: one-hot B^T rows select columns of A
+    a_bits = rand_bf16(rng, m, k)
+    b1 = np.zeros((n, k), np.float32)
+    for j, kk in picks:
+        b1[j, kk] = 1.0
+    c = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(oracle.to_bf16(b1)),
+                       flags=gemm.make_flags(variant)).cpu().numpy()
+    expect = np.zeros((m, n), np.float32)
+    for j, kk in picks:
+        expect[:, j] = oracle.of_bf16(a_bits)[:, kk]
+    assert np.array_equal(c, expect)
+
+
+def test_tf32_inputs_are_truncated_not_rounded():
+    """run_gemm_h100.cu:40-44 models the matrix unit as dropping the low 13
+    mantissa bits.  Probe with one-hot rows so each output is a single product."""
+    m = n = 256
+    k = 32
+    vals = np.array([0x3F801FFF, 0x3F802000, 0x3F803FFF, 0xBF801FFF, 0x3DCCCCCD, 0x477FFFFF],
+                    np.uint32).view(np.float32)
+    bt = np.zeros((n, k), np.float32)
+    bt[np.arange(len(vals)), np.arange(len(vals))] = vals
+    a = np.zeros((m, k), np.float32)
+    a[0, :len(vals)] = 1.0
+    a[1, :len(vals)] = vals          # both operands truncated
+    c = gemm.gemm_tf32(torch.from_numpy(a).to(DEV), torch.from_numpy(bt).to(DEV),
+                       flags=gemm.make_flags("1cta_128x128")).cpu().numpy()
+    expect = oracle.gemm_kmajor(a, bt, oracle.MODE_TF32)
+    assert np.array_equal(c[:2, :len(vals)].view(np.uint32), expect[:2, :len(vals)].view(np.uint32))
+
+
+# ---- ring depth / barrier parity sweep ----------------------------------------------
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+@pytest.mark.parametrize("kblocks", [1, 2, 3, 4, 5, 8, 16, 17])
+def test_ring_and_parity_sweep_bf16(variant, kblocks):
+    rng = np.random.default_rng(kblocks)
+    m, n, k = 512, 768, 64 * kblocks
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    for stages in (2, 0):
+        c = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits),
+                           flags=gemm.make_flags(variant, stages=stages))
+        check_bf16(a_bits, bt_bits, c)
+
+
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+def test_many_tiles_per_cta_and_accumulator_reuse(variant):
+    """More tiles than CTAs: both TMEM accumulators are reused several times."""
+    rng = np.random.default_rng(5)
+    m, n, k = 4096, 4096, 128
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    c = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), flags=gemm.make_flags(variant))
+    exact = gemm.gemm_exact(bf16_tensor(a_bits), bf16_tensor(bt_bits), gemm.INPUT_BF16)
+    tol = strict_tol(k, float(np.abs(oracle.of_bf16(a_bits)).max()), float(np.abs(oracle.of_bf16(bt_bits)).max()))
+    assert float((c - exact).abs().max()) <= tol
+    rows = np.array([0, 127, 128, 2049, 4095], np.int32)
+    check_bf16(a_bits, bt_bits, c, rows=rows)
+
+
+# ---- ragged shapes and guard bands ----------------------------------------------------
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+@pytest.mark.parametrize("m,n,k", [(100, 72, 40), (129, 260, 72), (300, 520, 200), (1, 4, 8)])
+def test_ragged_shapes_bf16(golden_dir, variant, m, n, k):
+    if (m, n, k) == (100, 72, 40):
+        g = np.load(os.path.join(golden_dir, "ragged_bf16_100x72x40.npz"))
+        a_bits, bt_bits = g["a_bits"], g["bt_bits"]
+    else:
+        rng = np.random.default_rng(m + n + k)
+        a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    # C sits inside a larger NaN-filled buffer: nothing outside [M,N] may be written
+    pad = torch.full((m + 2, n + 8), float("nan"), device=DEV)
+    c = pad[1:m + 1, 4:n + 4]
+    gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), c, flags=gemm.make_flags(variant))
+    check_bf16(a_bits, bt_bits, c.contiguous())
+    assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
+    assert torch.isnan(pad[:, :4]).all() and torch.isnan(pad[:, n + 4:]).all()
+
+
+def test_ragged_tf32():
+    rng = np.random.default_rng(9)
+    m, n, k = 200, 136, 52
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    bt = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+    for variant in TC_VARIANTS:
+        c = gemm.gemm_tf32(torch.from_numpy(a).to(DEV), torch.from_numpy(bt).to(DEV),
+                           flags=gemm.make_flags(variant)).cpu().numpy()
+        expect = oracle.gemm_kmajor(a, bt, oracle.MODE_TF32)
+        assert np.abs(c - expect).max() <= strict_tol(k, 1.0, 1.0), variant
+
+
+def test_strided_operands():
+    rng = np.random.default_rng(21)
+    m, n, k = 256, 256, 128
+    a_bits, bt_bits = rand_bf16(rng, m, k + 64), rand_bf16(rng, n, k + 8)
+    ta, tb = bf16_tensor(a_bits)[:, :k], bf16_tensor(bt_bits)[:, :k]
+    c = gemm.gemm_bf16(ta, tb)
+    check_bf16(np.ascontiguousarray(a_bits[:, :k]), np.ascontiguousarray(bt_bits[:, :k]), c)
+
+
+# ---- split-K --------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k,splits", [(128, 1024, 2048, 4), (128, 1024, 2048, 0), (100, 264, 1000, 3),
+                                          (256, 512, 64, 5)])
+def test_split_k(m, n, k, splits):
+    rng = np.random.default_rng(splits + k)
+    a_bits, bt_bits = rand_bf16(rng, m, k, 0.02), rand_bf16(rng, n, k, 0.02)
+    c = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits),
+                       flags=gemm.make_flags("splitk", splits=splits))
+    check_bf16(a_bits, bt_bits, c)
+
+
+# ---- helpers ---------------------------------------------------------------------------
+def test_conversion_and_transpose_match_the_oracle(golden_dir):
+    g = np.load(os.path.join(golden_dir, "rounding_edges.npz"))
+    x = g["bits"].view(np.float32)
+    got = gemm.f32_to_bf16(torch.from_numpy(x.copy()).to(DEV)).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, g["bf16"])
+    rng = np.random.default_rng(2)
+    b = rng.standard_normal((70, 45)).astype(np.float32)
+    assert np.array_equal(gemm.transpose(torch.from_numpy(b).to(DEV)).cpu().numpy(), b.T)
+    b16 = oracle.to_bf16(b)
+    got = gemm.transpose(bf16_tensor(b16)).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, b16.T)
+
+
+def test_device_generators():
+    u = torch.empty(1 << 16, device=DEV)
+    gemm.fill_uniform(u, 5, 100)
+    assert np.array_equal(u.cpu().numpy(), synth.uniform_pm1(5, 1 << 16, offset=100))
+    z = torch.empty(1 << 20, device=DEV)
+    gemm.fill_normal(z, 2, 1.0)
+    zh = synth.normal(2, 1 << 20)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1.0) < 0.01
+    assert np.abs(z.cpu().numpy() - zh).max() < 1e-4     # same stream, libm-level differences only
+    zb = torch.empty(1 << 16, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(zb, 3, 0.02)
+    assert abs(float(zb.float().std()) - 0.02) < 1e-3
+
+
+def test_bounded_wait_gives_up_and_reports(oxlib):
+    """A wait on a barrier nothing arrives on must time out, return and leave a
+    status the host can read; the device stays usable."""
+    st = oxlib.oxgpu_b200_selftest_bounded_wait(2_000_000)    # 2 ms budget
+    assert st == -7
+    assert b"kind 6" in oxlib.oxgpu_b200_last_error()
+    assert gemm.device_status()[0] == 0                        # cleared by the read
+    x = torch.ones(8, device=DEV)
+    assert float(x.sum()) == 8.0
+
+
+def test_host_buffer_entry_point():
+    rng = np.random.default_rng(31)
+    m, n, k = 1000, 520, 328
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    a_h = torch.from_numpy(a_bits.view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+    b_h = torch.from_numpy(bt_bits.view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+    c_h = torch.full((m, n), float("nan")).pin_memory()
+    for _ in range(2):
+        gemm.gemm_bf16_host(a_h, b_h, c_h)
+        check_bf16(a_bits, bt_bits, c_h)
+    a32 = rng.uniform(-1, 1, (300, 64)).astype(np.float32)
+    b32 = rng.uniform(-1, 1, (260, 64)).astype(np.float32)
+    c32 = torch.empty(300, 260)
+    gemm.gemm_tf32_host(torch.from_numpy(a32), torch.from_numpy(b32), c32)
+    expect = oracle.gemm_kmajor(a32, b32, oracle.MODE_TF32)
+    assert np.abs(c32.numpy() - expect).max() <= strict_tol(64, 1.0, 1.0)
+
+
+# ---- the workload configurations at full size ---------------------------------------------
+def _sample_rows(m, count, seed):
+    rng = np.random.default_rng(seed)
+    rows = np.unique(np.concatenate([[0, m - 1, 127, 128], rng.integers(0, m, count)])).astype(np.int32)
+    return rows
+
+
+def test_tf32_4096_cubed():
+    """TF32 4096^3, uniform[-1,1) seed 1: sampled rows against the CPU oracle,
+    the whole matrix against the exact device kernel (itself bit-identical to
+    the oracle), and linearity C(2A) == 2 C(A) exactly."""
+    n = 4096
+    a = torch.empty(n, n, device=DEV)
+    b = torch.empty(n, n, device=DEV)
+    gemm.fill_uniform(a, 1, 0)
+    gemm.fill_uniform(b, 1, n * n)
+    bt = gemm.transpose(b)
+    c = gemm.gemm_tf32(a, bt)
+    tol = tc_tol(n, 1.0, 1.0)
+    rows = _sample_rows(n, 12, 1)
+    expect = oracle.gemm_kmajor(a[rows].cpu().numpy(), bt.cpu().numpy(), oracle.MODE_TF32,
+                                threads=oracle.max_threads())
+    assert np.abs(c[rows].cpu().numpy() - expect).max() <= tol
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_TF32)
+    assert np.array_equal(exact[rows].cpu().numpy(), expect)
+    assert float((c - exact).abs().max()) <= tol
+    c2 = gemm.gemm_tf32(a * 2, bt)
+    assert torch.equal(c2, c * 2)
+
+
+def test_bf16_8192_cubed():
+    """bf16 8192^3, normal(0,1) seed 2, A row-major / B column-major."""
+    n = 8192
+    a = torch.empty(n, n, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(n, n, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 2, 1.0, 0)
+    gemm.fill_normal(bt, 2, 1.0, n * n)
+    c = gemm.gemm_bf16(a, bt)
+    a_max, b_max = float(a.float().abs().max()), float(bt.float().abs().max())
+    tol = tc_tol(n, a_max, b_max)
+    rows = _sample_rows(n, 4, 2)
+    a_bits = a[rows].view(torch.int16).cpu().numpy().view(np.uint16)
+    bt_bits = bt.view(torch.int16).cpu().numpy().view(np.uint16)
+    expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits, threads=oracle.max_threads())
+    assert np.abs(c[rows].cpu().numpy() - expect).max() <= tol
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
+    assert np.array_equal(exact[rows].cpu().numpy(), expect)
+    assert float((c - exact).abs().max()) <= tol
+    for variant in ("1cta_128x256", "2cta_256x128"):
+        cv = gemm.gemm_bf16(a, bt, flags=gemm.make_flags(variant))
+        assert float((cv - exact).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("m,n,k", [(8192, 28672, 8192), (8192, 8192, 28672), (128, 8192, 8192)])
+def test_bf16_projection_shapes(m, n, k):
+    """bf16 rectangular projection shapes, normal(0, 0.02) seed 3."""
+    a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 3, 0.02, 0)
+    gemm.fill_normal(bt, 3, 0.02, m * k)
+    c = gemm.gemm_bf16(a, bt)
+    tol = tc_tol(k, float(a.float().abs().max()), float(bt.float().abs().max()))
+    rows = _sample_rows(m, 2, 3)[:4]
+    a_bits = a[rows].view(torch.int16).cpu().numpy().view(np.uint16)
+    bt_bits = bt.view(torch.int16).cpu().numpy().view(np.uint16)
+    expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits, threads=oracle.max_threads())
+    assert np.abs(c[rows].cpu().numpy() - expect).max() <= tol
+    if m == 128:
+        cs = gemm.gemm_bf16(a, bt, flags=gemm.make_flags("splitk"))
+        assert np.abs(cs[rows].cpu().numpy() - expect).max() <= tol
+        exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
+        assert float((c - exact).abs().max()) <= tol and float((cs - exact).abs().max()) <= tol
+
+
+def test_launch_count_increases():
+    before = gemm.launch_count()
+    a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    gemm.gemm_bf16(a, a)
+    assert gemm.launch_count() == before + 1

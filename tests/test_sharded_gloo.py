@@ -1,0 +1,103 @@
+"""Host-side logic of the column-sharded multi-GPU driver, on CPU: partitioning,
+and a world_size-2 gloo run in which each rank computes its shard with the
+oracle, the shards are all-gathered and re-interleaved, and the result equals
+the unsharded oracle bit for bit."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oxcamlgpu_b200 import sharded
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("n,world", [(65536, 1), (65536, 2), (65536, 4), (65536, 8), (8192, 8), (2048, 8),
+                                     (1000, 3), (256, 4), (28672, 8)])
+def test_column_partition(n, world):
+    parts = sharded.column_partition(n, world)
+    assert len(parts) == world and parts[0][0] == 0 and parts[-1][1] == n
+    covered = 0
+    for lo, hi in parts:
+        assert lo == covered and hi >= lo
+        assert lo % 256 == 0
+        covered = hi
+    assert covered == n
+    widths = [hi - lo for lo, hi in parts]
+    # at most one aligned block apart (the ragged tail may shorten the last one further)
+    assert max(widths) - min(widths) < 2 * 256
+    if n % (256 * world) == 0:
+        assert len(set(widths)) == 1 and widths[0] == n // world
+
+
+def test_partition_rejects_nonsense():
+    with pytest.raises(ValueError):
+        sharded.column_partition(0, 2)
+    with pytest.raises(ValueError):
+        sharded.column_partition(10, 0)
+
+
+def test_blocks_to_row_major():
+    g = torch.arange(2 * 3 * 4).reshape(2, 3, 4)
+    c = sharded.blocks_to_row_major(g)
+    assert c.shape == (3, 8)
+    assert torch.equal(c[:, :4], g[0]) and torch.equal(c[:, 4:], g[1])
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, failures):
+    try:
+        sys.path.insert(0, ROOT)
+        import oracle
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        m, n, k = 48, 512, 96
+        rng = np.random.default_rng(0)                       # same operands on every rank
+        a_bits = oracle.to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+        bt_bits = oracle.to_bf16(rng.standard_normal((n, k)).astype(np.float32))
+        bt_shard = sharded.shard_rows_of_bt(torch.from_numpy(bt_bits.view(np.int16)), rank, world)
+        n0, n1 = sharded.column_partition(n, world)[rank]
+        assert bt_shard.shape[0] == n1 - n0 == n // world
+        c_shard = oracle.gemm_kmajor_bf16(a_bits, bt_shard.numpy().view(np.uint16))
+        gathered = sharded.all_gather_c(torch.from_numpy(c_shard))
+        assert gathered.shape == (world, m, n // world)
+        full = sharded.blocks_to_row_major(gathered).numpy()
+        expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits)
+        assert np.array_equal(full.view(np.uint32), expect.view(np.uint32))
+        # max-over-ranks timing reduction used by the bench
+        t = torch.tensor([1.0 + rank])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert float(t) == float(world)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover - reported through the queue
+        failures.put(f"rank {rank}: {e!r}")
+        raise
+
+
+def test_two_ranks_gloo_shard_gather_reassemble():
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    assert not msgs, msgs
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
