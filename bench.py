@@ -45,7 +45,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, from one ncu
 # capture of the same kernel (profiles/umma_gemm_bf16_8192.md); None = not captured.
-NCU_TRAFFIC_BYTES = {"bf16_8192": None}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 1.519e9}
 
 
 def measured_peaks():
@@ -59,7 +59,7 @@ def measured_peaks():
 
 class ClockSampler:
     """Samples SM clock, power and throttle reasons through NVML (read-only)
-    every 100 ms while the timed region runs."""
+    every 20 ms while the device-timed windows run."""
 
     def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -89,7 +89,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.02)
 
     def __enter__(self):
         if self.nv:
@@ -309,8 +309,8 @@ def main():
 
     sampler = ClockSampler(local)
     launches0 = gemm.launch_count()
-    with sampler:
-        ours_ms = timed_steps(run_gemm, args.steps, args.warmup)
+    sampler.__enter__()
+    ours_ms = timed_steps(run_gemm, args.steps, args.warmup)
     launches = gemm.launch_count() - launches0 - args.warmup
     total_ms = reduce_max(sum(ours_ms))
     ms_per_step = total_ms / args.steps
@@ -327,6 +327,7 @@ def main():
     cublas_mean = reduce_max(sum(cublas_ms) / args.steps)
     ours2_ms = timed_steps(run_gemm, args.steps, 2)        # second window after cuBLAS (interleaved)
     ours2_med = reduce_max(statistics.median(ours2_ms))
+    sampler.__exit__()
     del c_ref
 
     gather_ms = None

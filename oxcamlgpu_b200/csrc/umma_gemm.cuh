@@ -356,7 +356,13 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int c_row0 = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) +
                          (int)cta_rank * BM_CTA + quad * 32;
       const int c_col0 = tn * BN;
-      if (!bounded_wait(tmem_full_bar + 8u * acc, acc_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w)) {
+      // one lane waits (the wait can last a whole main loop); the rest of the
+      // warp parks at the shuffle instead of polling the barrier
+      uint32_t got = 0;
+      if (lane == 0)
+        got = bounded_wait(tmem_full_bar + 8u * acc, acc_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
         ok = false;
         break;
       }
