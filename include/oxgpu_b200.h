@@ -165,6 +165,38 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
                                       unsigned flags, void *workspace, size_t workspace_bytes,
                                       void *stream);
 
+/* Split-K bf16 GEMM that allocates nothing.  (No counterpart in the reference:
+ * its kernels use no scratch memory at all.)
+ *
+ * For callers that cannot obtain device memory at call time: a process whose
+ * device memory is handed out up front by its own arena or by a fixed
+ * per-tenant budget, so a late cudaMalloc may fail or is simply not permitted;
+ * or a latency-sensitive loop that cannot afford the implicit device-wide
+ * synchronisation an allocation or free may cause.  Such a caller passes only
+ * its inputs and output; the f32 partial tiles of the K slices live in a
+ * fixed array inside the library, OXGPU_STATIC_SCRATCH_BYTES (32 MiB) of device
+ * memory that every GPU loading the library holds until the process exits.
+ *
+ * Same arithmetic and kernels as oxgpu_b200_gemm_bf16_ws with
+ * OXGPU_VARIANT_SPLITK; `splits` = number of K slices (0: chosen by the
+ * library, at most 16).  The slices need splits * roundup(m,128) * n * 4 bytes;
+ * if that exceeds OXGPU_STATIC_SCRATCH_BYTES the call returns OXGPU_E_TOO_LARGE
+ * and launches nothing (e.g. m=128, n=8192 allows up to 8 slices).  n % 4 == 0.
+ *
+ * The first call on each device looks up the array's device address (with that
+ * device current); make that first call before starting any stream capture.
+ * Neither that set-up nor any later call uses cudaMalloc, cudaFree or an
+ * allocating library routine.  All calls on a device share the one array and it
+ * keeps whatever the previous call left in it; that is harmless here, because
+ * every element the reduction reads is overwritten by the same call first, so
+ * nothing needs clearing.  Two calls whose kernels overlap on the same GPU
+ * (different streams, or different host threads) race on the array: issue them
+ * on one stream or otherwise order them. */
+#define OXGPU_STATIC_SCRATCH_BYTES (32u << 20)
+OXGPU_API int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16_t *bt, float *c,
+                                                 int m, int n, int k, int64_t lda, int64_t ldb,
+                                                 int64_t ldc, int splits, void *stream);
+
 /* Exact GEMM on CUDA cores: one f32 accumulator per output, k ascending, a
  * rounded multiply then a rounded add (never fused) -- the arithmetic of the
  * host reference loop (test/hardware/run_gemm_h100.cu:150-162), so the result

@@ -499,6 +499,61 @@ int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, float *c, int
                       (cudaStream_t)stream);
 }
 
+// ---- split-K without any allocation ------------------------------------------------
+// The partial tiles live in this file-scope device array.  In host code the
+// array's name is only a stand-in, not a device address, so its address is
+// looked up once per device with cudaGetSymbolAddress and that pointer is what
+// the kernels receive (through the workspace tensor map and the reduction's
+// argument).
+static __device__ __align__(256) float g_static_splitk_scratch[OXGPU_STATIC_SCRATCH_BYTES / sizeof(float)];
+static float *g_static_scratch_addr[64];  // per device; filled on the first call there
+
+int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16_t *bt, float *c, int m, int n,
+                                       int k, int64_t lda, int64_t ldb, int64_t ldc, int splits,
+                                       void *stream) {
+  int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, 2);
+  if (st) return st;
+  if (splits < 0 || splits > 255) return fail(OXGPU_E_INVALID_ARG, "splits must be in [0, 255]");
+  if (n % 4) return fail(OXGPU_E_SHAPE, "split-K needs N to be a multiple of 4");
+  int dev_index;
+  DeviceState *dev;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  // the slice count the split-K path will settle on (same rule as the
+  // workspace entry point), so the size can be refused before anything runs
+  const int num_kb = (k + 63) / 64;
+  if (splits == 0) {
+    long long tiles = (long long)((m + 127) / 128) * ((n + 127) / 128);
+    splits = (int)((2LL * dev->sm_count + tiles - 1) / tiles);
+    if (splits > 16) splits = 16;
+  }
+  if (splits > num_kb) splits = num_kb;
+  if (splits < 1) splits = 1;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per - 1) / kb_per;
+  const size_t m_pad = (size_t)((m + 127) / 128) * 128;
+  const size_t need = (size_t)splits * m_pad * (size_t)n * sizeof(float);
+  if (need > (size_t)OXGPU_STATIC_SCRATCH_BYTES) {
+    char text[200];
+    std::snprintf(text, sizeof text,
+                  "split-K partial tiles need %zu bytes (%d slices x %zu rows x %d columns), the "
+                  "built-in scratch holds %u: use fewer slices or the workspace entry point",
+                  need, splits, m_pad, n, (unsigned)OXGPU_STATIC_SCRATCH_BYTES);
+    return fail(OXGPU_E_TOO_LARGE, text);
+  }
+  if (!g_static_scratch_addr[dev_index]) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_static_scratch_addr[dev_index]) {
+      float *addr = nullptr;
+      OX_CUDA(cudaGetSymbolAddress((void **)&addr, g_static_splitk_scratch));
+      if (!addr) return fail(OXGPU_E_INVALID_ARG, "cudaGetSymbolAddress returned a null address");
+      g_static_scratch_addr[dev_index] = addr;
+    }
+  }
+  const unsigned flags = OXGPU_FLAG_VARIANT(OXGPU_VARIANT_SPLITK) | OXGPU_FLAG_SPLITS(splits);
+  return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, g_static_scratch_addr[dev_index],
+                      (size_t)OXGPU_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}
+
 int oxgpu_b200_gemm_exact(const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
                           int64_t ldb, int64_t ldc, int input_mode, void *stream) {
   if (!a || !bt || !c) return fail(OXGPU_E_INVALID_ARG, "null operand pointer");

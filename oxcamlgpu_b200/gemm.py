@@ -129,6 +129,26 @@ def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, 
     return c
 
 
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def gemm_bf16_splitk_static(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor, splits: int = 0,
+                            stream=None) -> torch.Tensor:
+    """Split-K bf16 GEMM for callers that cannot allocate device memory at call
+    time (memory handed out up front by an arena or a fixed budget, or a loop
+    that cannot tolerate an allocation's device-wide synchronisation): the K
+    slices' partial tiles go to a fixed 32 MiB array inside the library instead
+    of a workspace, so the caller passes only A, B^T and C.  Raises OxgpuError
+    (status -6) when the slices would not fit.  Calls that overlap on one GPU
+    race on that array; keep them on one stream."""
+    m, n, k = _check_operands(a, bt, torch.bfloat16)
+    c = _out(c, m, n, a.device)
+    check(lib().oxgpu_b200_gemm_bf16_splitk_static(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k,
+                                                   a.stride(0), bt.stride(0), c.stride(0), splits,
+                                                   ctypes.c_void_p(_stream(stream))))
+    return c
+
+
 def gemm_tf32(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
               stream=None) -> torch.Tensor:
     """C = A * B with f32 A[M,K], B^T[N,K] rounded to TF32 by the matrix unit
