@@ -327,6 +327,14 @@ def main():
     cublas_mean = reduce_max(sum(cublas_ms) / args.steps)
     ours2_ms = timed_steps(run_gemm, args.steps, 2)        # second window after cuBLAS (interleaved)
     ours2_med = reduce_max(statistics.median(ours2_ms))
+    cublas_f32_med = None
+    if kind == "bf16":
+        # the same work as ours: bf16 operands, f32 C (cuBLASLt through torch.mm's out_dtype)
+        try:
+            f32_ms = timed_steps(lambda: torch.mm(a, bt_t, out_dtype=torch.float32), args.steps, 3)
+            cublas_f32_med = reduce_max(statistics.median(f32_ms))
+        except Exception:
+            cublas_f32_med = None
     sampler.__exit__()
     del c_ref
 
@@ -405,7 +413,9 @@ def main():
                        "tflops_at_median": flops_all / (cublas_med * 1e-3) * 1e-12,
                        "ours_over_cublas_median": cublas_med / median_ms,
                        "ours_second_window_median_ms": ours2_med,
-                       "ours_over_cublas_second_window": cublas_med / ours2_med},
+                       "ours_over_cublas_second_window": cublas_med / ours2_med,
+                       "f32_out_median_ms": cublas_f32_med,
+                       "ours_over_cublas_f32_out": (cublas_f32_med / median_ms) if cublas_f32_med else None},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": sampler.summary(),
             "check": {"max_abs_err_sampled_rows": err, "tolerance": tol},

@@ -135,12 +135,17 @@ enum {
   OXGPU_VARIANT_1CTA_256x128 = 3, /* one CTA, two UMMA 128x128 sharing B */
   OXGPU_VARIANT_2CTA_256x256 = 4, /* CTA pair, cta_group::2 UMMA 256x256 */
   OXGPU_VARIANT_2CTA_256x128 = 5,
-  OXGPU_VARIANT_SPLITK = 6        /* 1-CTA 128x128 tiles over K slices + reduce; needs workspace */
+  OXGPU_VARIANT_SPLITK = 6,       /* 1-CTA 128x128 tiles over K slices + reduce; needs workspace */
+  OXGPU_VARIANT_2CTA_512x256 = 7  /* CTA pair, 256 rows per CTA: two UMMA 256x256 per K step */
 };
 #define OXGPU_FLAG_VARIANT(v) ((unsigned)(v) & 0xffu)
 #define OXGPU_FLAG_STAGES(s) (((unsigned)(s) & 0xfu) << 8)    /* 0 = deepest that fits */
 #define OXGPU_FLAG_GROUP_M(g) (((unsigned)(g) & 0xffu) << 12) /* 0 = 16, the reference's */
 #define OXGPU_FLAG_SPLITS(s) (((unsigned)(s) & 0xffu) << 20)  /* 0 = chosen by the library */
+/* Tiles with two row blocks per CTA (256-row variants): K blocks issued
+ * block-major at either end of a tile so the epilogue overlaps; 0 = library
+ * default, 15 = never, else that many K blocks. */
+#define OXGPU_FLAG_REORDER(g) (((unsigned)(g) & 0xfu) << 28)
 
 /* Buffer entry points: the library encodes its own maps, so it may pick any
  * variant (2-CTA tiles, ragged edges).  a: [M,K] row-major with leading

@@ -23,7 +23,7 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kKinds = 2;     // 0 = bf16, 1 = tf32
-constexpr int kVariants = 6;  // index by Variant value (1..5 used)
+constexpr int kVariants = 8;  // index by Variant value (1..5 and 7 used)
 
 std::atomic<uint64_t> g_launches{0};
 
@@ -101,7 +101,8 @@ int current_device(int *dev, DeviceState **state) {
 }
 
 int encode_2d(CUtensorMap *map, const void *ptr, int element_bytes, uint64_t dim0, uint64_t dim1,
-              uint64_t stride1_bytes, uint32_t box0, uint32_t box1) {
+              uint64_t stride1_bytes, uint32_t box0, uint32_t box1,
+              CUtensorMapL2promotion promotion = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
   int st = resolve_driver();
   if (st) return st;
   CUtensorMapDataType dt;
@@ -113,8 +114,8 @@ int encode_2d(CUtensorMap *map, const void *ptr, int element_bytes, uint64_t dim
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promotion,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char text[200];
     std::snprintf(text, sizeof text,
@@ -135,6 +136,7 @@ const void *kernel_for(int kind, int variant) {
       case VARIANT_1CTA_256x128: return OX_K(0, 256, 128, 1);
       case VARIANT_2CTA_256x256: return OX_K(0, 128, 256, 2);
       case VARIANT_2CTA_256x128: return OX_K(0, 128, 128, 2);
+      case VARIANT_2CTA_512x256: return OX_K(0, 256, 256, 2);
     }
   } else {
     switch (variant) {
@@ -143,6 +145,7 @@ const void *kernel_for(int kind, int variant) {
       case VARIANT_1CTA_256x128: return OX_K(1, 256, 128, 1);
       case VARIANT_2CTA_256x256: return OX_K(1, 128, 256, 2);
       case VARIANT_2CTA_256x128: return OX_K(1, 128, 128, 2);
+      case VARIANT_2CTA_512x256: return OX_K(1, 256, 256, 2);
     }
   }
 #undef OX_K
@@ -162,7 +165,11 @@ unsigned long long wait_budget_ns() {
 struct LaunchPlan {
   int kind, variant, stages, group_m;
   int splits, kb_per_split, split_row_stride;
+  int reorder_kb = -1;  // -1: library default
 };
+
+// K blocks issued block-major at either end of a tile (two-row-block tiles).
+constexpr int kDefaultReorderKb = 3;
 
 // Launch one tcgen05 GEMM.  Maps are either inside `p` (by value) or behind
 // p.a_map_ptr / p.b_map_ptr.
@@ -182,11 +189,15 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   p.tiles_n = (n + shape.tile_n - 1) / shape.tile_n;
   p.num_k_blocks = (k + kbe - 1) / kbe;
   p.stages = stages;
-  p.group_m = plan.group_m > 0 ? plan.group_m : 16;
+  // Group height of the tile order.  The reference uses 16 tile-rows of 128;
+  // with 256- and 512-row tiles and 74 CTA pairs in flight, 8 tile-rows keep the
+  // wave closest to square (fewest distinct operand blocks per wave).
+  p.group_m = plan.group_m > 0 ? plan.group_m : (shape.tile_m >= 256 ? 8 : 16);
   p.k_block_elems = kbe;
   p.splits = plan.splits > 0 ? plan.splits : 1;
   p.kb_per_split = plan.splits > 1 ? plan.kb_per_split : p.num_k_blocks;
   p.split_row_stride = plan.split_row_stride;
+  p.reorder_kb = plan.reorder_kb >= 0 ? plan.reorder_kb : kDefaultReorderKb;
   p.wait_budget_ns = wait_budget_ns();
 
   bool &attr = dev.attr_set[plan.kind][plan.variant];
@@ -255,6 +266,11 @@ int choose_variant(const DeviceState &dev, int m, int n, int k) {
   (void)k;
   auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
   const int pairs = dev.sm_count / 2;
+  // The 512x256 pair tile moves a quarter less operand data per flop than
+  // 256x256 (48 instead of 64 bytes per clock per SM at full tensor rate), which
+  // is what limits the kernel at boost clocks: 95 % against 91.5 % of cuBLAS at
+  // bf16 8192^3, even though it cannot double-buffer its accumulator.
+  if (tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
   if (tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
   if (tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
   if (tiles(128, 256) >= dev.sm_count / 2) return VARIANT_1CTA_128x256;
@@ -278,12 +294,14 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   const bool splitk = variant == VARIANT_SPLITK;
   if (variant == VARIANT_AUTO) variant = choose_variant(*dev, m, n, k);
   if (splitk) variant = VARIANT_1CTA_128x128;
-  if (variant < VARIANT_1CTA_128x256 || variant > VARIANT_2CTA_256x128)
+  if (variant_shape(variant).cta_group == 0)
     return fail(OXGPU_E_INVALID_ARG, "unknown variant in flags");
   const VariantShape shape = variant_shape(variant);
   const int kbe = kind == 0 ? 64 : 32;
 
   LaunchPlan plan{kind, variant, stages, group_m, 1, 0, 0};
+  const int reorder_field = (int)((flags >> 28) & 0xfu);  // 0 default, 15 off, else that many K blocks
+  plan.reorder_kb = reorder_field == 0 ? -1 : (reorder_field == 15 ? 0 : reorder_field);
   GemmParams p;
   std::memset(&p, 0, sizeof p);
   const int a_box = shape.cta_a_rows, b_box = shape.cta_b_rows;
@@ -705,7 +723,7 @@ uint64_t oxgpu_b200_launch_count(void) { return g_launches.load(std::memory_orde
 
 const char *oxgpu_b200_build_info(void) {
   return "oxgpu_b200: sm_100a; tcgen05 UMMA bf16+tf32; variants 1cta_128x256 1cta_128x128 "
-         "1cta_256x128 2cta_256x256 2cta_256x128 splitk; cudart " OXGPU_STRINGIFY(CUDART_VERSION);
+         "1cta_256x128 2cta_256x256 2cta_256x128 2cta_512x256 splitk; cudart " OXGPU_STRINGIFY(CUDART_VERSION);
 }
 
 }  // extern "C"

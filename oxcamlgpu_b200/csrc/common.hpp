@@ -26,16 +26,17 @@ enum Variant {
   VARIANT_2CTA_256x256 = 4,
   VARIANT_2CTA_256x128 = 5,
   VARIANT_SPLITK = 6,
+  VARIANT_2CTA_512x256 = 7,
 };
 
-// Every tcgen05 GEMM kernel here runs 6 warps: TMA producer, MMA issuer (also
-// owns the TMEM allocation), and four epilogue warps (one per TMEM lane
+// Every tcgen05 GEMM kernel here runs 10 warps: TMA producer, MMA issuer (also
+// owns the TMEM allocation), and eight epilogue warps (two per TMEM lane
 // quadrant).
-constexpr int kThreadsPerCta = 192;
+constexpr int kThreadsPerCta = 320;
 // Largest dynamic shared window a CTA may opt into on sm_100 (227 KiB).
 constexpr int kMaxDynamicSmem = 232448;
-// Per-warp epilogue staging: two 32x32 f32 sub-tiles (4 KiB each) x 4 warps.
-constexpr int kEpilogueStagingBytes = 4 * 2 * 4096;
+// Per-warp epilogue staging: one 32x32 f32 sub-tile (4 KiB) x 8 warps.
+constexpr int kEpilogueStagingBytes = 8 * 4096;
 // Barriers + TMEM base slot, padded.
 constexpr int kBarrierRegionBytes = 1024;
 // Stage bases must be 1024-byte aligned for the 128-byte swizzle atoms; the
@@ -63,6 +64,7 @@ inline VariantShape variant_shape(int variant) {
     case VARIANT_1CTA_256x128: return {1, 256, 128, 256, 128};
     case VARIANT_2CTA_256x256: return {2, 256, 256, 128, 128};
     case VARIANT_2CTA_256x128: return {2, 256, 128, 128, 64};
+    case VARIANT_2CTA_512x256: return {2, 512, 256, 256, 128};
     default: return {0, 0, 0, 0, 0};
   }
 }

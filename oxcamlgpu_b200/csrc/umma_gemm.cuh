@@ -11,15 +11,18 @@
 //   warp 0      TMA producer      one lane issues cp.async.bulk.tensor loads
 //   warp 1      UMMA issuer       one lane issues tcgen05.mma; the warp owns the
 //                                 TMEM allocation
-//   warps 2-5   epilogue          tcgen05.ld TMEM -> registers -> swizzled
-//                                 shared staging -> TMA store to C
+//   warps 2-9   epilogue          tcgen05.ld TMEM -> registers -> swizzled
+//                                 shared staging -> TMA store to C (two groups
+//                                 of four warps, one warp per TMEM lane quadrant)
 //
 // The kernel is persistent: each CTA (or CTA pair) walks tiles
-// first, first+stride, ... in the grouped order, and keeps two accumulators in
-// TMEM so the epilogue of tile i overlaps the main loop of tile i+1.  In the
-// CTA-pair variants (cta_group::2) each CTA stages its own 128 rows of A and
-// its own half of the B^T rows, the leader CTA issues UMMAs that read both
-// CTAs' shared memory, and no load is multicast.
+// first, first+stride, ... in the grouped order.  Where the tile's accumulator
+// takes at most half of TMEM, two accumulator sets alternate so the epilogue of
+// tile i overlaps the main loop of tile i+1; the largest tile (256 rows x 256
+// columns per CTA) fills TMEM and trades that overlap for a quarter less
+// operand traffic per flop.  In the CTA-pair variants (cta_group::2) each CTA
+// stages its own rows of A and its own half of the B^T rows, the leader CTA
+// issues UMMAs that read both CTAs' shared memory, and no load is multicast.
 //
 // Every wait is bounded: when a wait outlives its budget the waiter records
 // where it gave up in the device status block, raises the CTA's abort flag and
@@ -64,6 +67,9 @@ struct GemmParams {
   // slice s stores its partial tile `split_row_stride` rows further down the C
   // map (a [splits * rows, N] workspace).  splits == 1: plain GEMM.
   int splits, kb_per_split, split_row_stride;
+  // Tiles with two row blocks per CTA: how many K blocks at either end of a tile
+  // are issued block-major (see the issuer); 0 = always interleaved.
+  int reorder_kb;
   unsigned long long wait_budget_ns;
 };
 
@@ -125,30 +131,40 @@ __host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
 template <int KIND, int BM_CTA, int BN, int CTA_GROUP>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
 umma_gemm_kernel(const __grid_constant__ GemmParams p) {
-  constexpr int MMA_M_COUNT = BM_CTA / 128;       // UMMAs along M per K step (1-CTA 256-row tile: 2)
-  constexpr int UMMA_M = 128 * CTA_GROUP;         // rows one instruction produces
+  // A CTA owns BM_CTA rows of the tile as MI blocks of 128 rows (one UMMA each
+  // per K step, all sharing the staged B^T rows).  Block `mi` of accumulator
+  // set `set` is one hand-off unit between the issuer and the epilogue.
+  constexpr int MI = BM_CTA / 128;
+  constexpr int UMMA_M = 128 * CTA_GROUP;         // rows one instruction produces (per pair)
   constexpr int B_ROWS = BN / CTA_GROUP;          // rows of B^T this CTA stages
-  constexpr int ACC_COLS = MMA_M_COUNT * BN;      // TMEM columns of one accumulator set
-  constexpr int TMEM_COLS = 2 * ACC_COLS;         // two sets: epilogue overlaps the next main loop
+  constexpr int ACC_COLS = MI * BN;               // TMEM columns of one accumulator set
+  constexpr int SETS = (2 * ACC_COLS <= 512) ? 2 : 1;  // two sets: epilogue overlaps next main loop
+  constexpr int TMEM_COLS = SETS * ACC_COLS;
+  constexpr int CHUNKS = BN / 32;                 // 32-column epilogue chunks per unit
+  // 8 epilogue warps form two groups; with MI == 2 group g drains block mi = g,
+  // with MI == 1 the groups split the unit's columns.
+  constexpr int CHUNKS_PER_GROUP = MI == 2 ? CHUNKS : CHUNKS / 2;
+  constexpr int EMPTY_ARRIVALS = (MI == 2 ? 4 : 8) * CTA_GROUP;
   constexpr uint32_t A_BYTES = BM_CTA * 128;
   constexpr uint32_t B_BYTES = B_ROWS * 128;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t IDESC = instr_desc<KIND>(UMMA_M, BN);
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
-  static_assert(BM_CTA == 128 || (BM_CTA == 256 && CTA_GROUP == 1), "unsupported tile");
+  static_assert(BM_CTA == 128 || BM_CTA == 256, "unsupported tile");
+  static_assert(CHUNKS_PER_GROUP >= 1 && CHUNKS % 2 == 0, "unsupported tile width");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = p.stages;
   const uint32_t staging_base = smem_base + (uint32_t)stages * STAGE_BYTES;
   const uint32_t bar_base = staging_base + kEpilogueStagingBytes;
-  // barrier region: full[stages], empty[stages], tmem_full[2], tmem_empty[2],
-  // drain, then the TMEM base slot and the abort flag.
+  // barrier region: full[8], empty[8], tmem_full[4], tmem_empty[4], drain,
+  // then the TMEM base slot and the abort flag.
   const uint32_t full_bar = bar_base;
   const uint32_t empty_bar = bar_base + 8u * kMaxStages;
   const uint32_t tmem_full_bar = bar_base + 16u * kMaxStages;
-  const uint32_t tmem_empty_bar = tmem_full_bar + 16u;
-  const uint32_t drain_bar = tmem_empty_bar + 16u;
+  const uint32_t tmem_empty_bar = tmem_full_bar + 32u;
+  const uint32_t drain_bar = tmem_empty_bar + 32u;
   const uint32_t tmem_slot = drain_bar + 8u;
   const uint32_t abort_slot = tmem_slot + 4u;
   uint8_t *const generic_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -178,10 +194,10 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
     }
-    for (int b = 0; b < 2; b++) {
-      ptx::mbar_init(tmem_full_bar + 8u * b, 1);
-      // one arrival per epilogue warp of every CTA that feeds this issuer
-      ptx::mbar_init(tmem_empty_bar + 8u * b, 4 * CTA_GROUP);
+    for (int u = 0; u < SETS * MI; u++) {
+      ptx::mbar_init(tmem_full_bar + 8u * u, 1);
+      // one arrival per epilogue warp (of every CTA feeding this issuer) that reads the unit
+      ptx::mbar_init(tmem_empty_bar + 8u * u, EMPTY_ARRIVALS);
     }
     ptx::mbar_init(drain_bar, 1);
     ptx::fence_mbar_init();
@@ -257,9 +273,7 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       if (!ok || *abort_ptr) {
         // Abort path: let the loads already issued land before shared memory
-        // is given up.  Slot s was last filled in the phase its full barrier
-        // is (or was) waiting on; both parities are tried with a short budget.
-        const WaitCtx drain{50ull * 1000 * 1000, abort_ptr};
+        // is given up (the leader's full barriers count both CTAs' bytes).
         if (CTA_GROUP == 1 || is_leader) {
           long long n = issued < stages ? issued : stages;
           for (long long i = 0; i < n; i++) {
@@ -267,7 +281,7 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint32_t ph = (uint32_t)(((issued - 1 - i) / stages) & 1);
             const uint64_t t0 = ptx::globaltimer_ns();
             while (!ptx::mbar_try_wait(full_bar + 8u * s, ph)) {
-              if (ptx::globaltimer_ns() - t0 > drain.budget_ns) break;
+              if (ptx::globaltimer_ns() - t0 > 50ull * 1000 * 1000) break;
             }
           }
         }
@@ -280,53 +294,114 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
+      // Four UMMAs (32 bytes of K each: 16 bf16 / 8 tf32) of K block `kb` for
+      // row block `mi`, reading ring slot `slot`.  The start address advances
+      // inside the swizzle span, as the reference does with its `+8*ki` /
+      // `+16*ki` element offsets (gemm.ml:121-125).
+      auto issue = [&](int slot, int mi, uint32_t d_tmem, bool first_block) {
+        const uint32_t a_addr = smem_base + (uint32_t)slot * STAGE_BYTES;
+        const uint64_t a_desc = smem_desc_sw128(a_addr) + (uint64_t)((mi * 128 * 128) >> 4);
+        const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+        for (int ki = 0; ki < 4; ki++)
+          ptx::umma<KIND, CTA_GROUP>(d_tmem + (uint32_t)(mi * BN), a_desc + (uint64_t)(ki * 2),
+                                     b_desc + (uint64_t)(ki * 2), IDESC, (!first_block || ki > 0) ? 1u : 0u);
+      };
+      auto release_slot = [&](int slot) {  // frees the ring slot once the UMMAs issued so far have read it
+        if constexpr (CTA_GROUP == 1) ptx::umma_commit(empty_bar + 8u * slot);
+        else ptx::umma_commit_pair(empty_bar + 8u * slot, 3);
+      };
+      auto publish = [&](int unit) {  // wakes the epilogue of every CTA holding rows of this unit
+        if constexpr (CTA_GROUP == 1) ptx::umma_commit(tmem_full_bar + 8u * unit);
+        else ptx::umma_commit_pair(tmem_full_bar + 8u * unit, 3);
+      };
+      // slot / parity of the i-th upcoming K block (i < stages)
+      auto slot_of = [&](int i) { return stage + i >= stages ? stage + i - stages : stage + i; };
+      auto phase_of = [&](int i) { return stage + i >= stages ? phase ^ 1u : phase; };
+      auto advance = [&]() {
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      };
       for (int w = cluster_id; ok && w < total_work; w += num_clusters, local_tile++) {
         const int sp = w % p.splits;
         const int kb_begin = sp * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
-        const int acc = local_tile & 1;
-        const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
-        if (!bounded_wait(tmem_empty_bar + 8u * acc, acc_phase ^ 1u, wctx, WAIT_TMEM_EMPTY,
-                          (uint32_t)w)) {
-          ok = false;
-          break;
+        const int set = local_tile % SETS;
+        const uint32_t set_phase = (uint32_t)(local_tile / SETS) & 1u;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(set * ACC_COLS);
+        // With two row blocks per CTA the first and last G K blocks of a tile
+        // are issued block-major (all of row block 0, then all of row block 1)
+        // instead of interleaved: at the end of a tile row block 0 is complete G
+        // block-times before row block 1, so its epilogue starts early, and at
+        // the start of the next tile row block 0 can accumulate again while row
+        // block 1 is still being drained.  The G slots involved stay occupied
+        // until the second pass has read them.
+        int G = 0;
+        if constexpr (MI == 2) {
+          G = p.reorder_kb;
+          if (G > stages - 1) G = stages - 1;
+          if (G > (kb_end - kb_begin) / 2) G = (kb_end - kb_begin) / 2;
         }
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-        for (int kb = kb_begin; kb < kb_end; kb++) {
+        int kb = kb_begin;
+        if (G > 0) {
+          // ---- head, row block 0 then row block 1 ----
+          ok = bounded_wait(tmem_empty_bar + 8u * (set * MI), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
+          for (int i = 0; ok && i < G; i++) {
+            ok = bounded_wait(full_bar + 8u * slot_of(i), phase_of(i), wctx, WAIT_FULL, (uint32_t)slot_of(i));
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            issue(slot_of(i), 0, d_tmem, i == 0);
+          }
+          if (ok) ok = bounded_wait(tmem_empty_bar + 8u * (set * MI + 1), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          for (int i = 0; i < G; i++) {
+            issue(stage, 1, d_tmem, i == 0);
+            release_slot(stage);
+            advance();
+          }
+          kb += G;
+        } else {
+          for (int mi = 0; ok && mi < MI; mi++)
+            ok = bounded_wait(tmem_empty_bar + 8u * (set * MI + mi), set_phase ^ 1u, wctx,
+                              WAIT_TMEM_EMPTY, (uint32_t)w);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+        }
+        // ---- body: row blocks interleaved per K block ----
+        for (; kb < kb_end - G; kb++) {
           if (!bounded_wait(full_bar + 8u * stage, phase, wctx, WAIT_FULL, (uint32_t)stage)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + (uint32_t)stage * STAGE_BYTES;
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
-          const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-          for (int ki = 0; ki < 4; ki++) {
-            // 32 bytes of K per instruction (16 bf16 / 8 tf32): advance the
-            // start address inside the swizzle span, as the reference does with
-            // its `+8*ki` / `+16*ki` element offsets (gemm.ml:121-125).
-            const uint64_t koff = (uint64_t)(ki * 2);
-#pragma unroll
-            for (int mi = 0; mi < MMA_M_COUNT; mi++) {
-              const uint64_t a_row_off = (uint64_t)((mi * 128 * 128) >> 4);
-              ptx::umma<KIND, CTA_GROUP>(d_tmem + (uint32_t)(mi * BN), a_desc + koff + a_row_off,
-                                         b_desc + koff, IDESC, (kb > kb_begin || ki > 0) ? 1u : 0u);
-            }
-          }
-          // frees the ring slot once these UMMAs have read it
-          if constexpr (CTA_GROUP == 1) ptx::umma_commit(empty_bar + 8u * stage);
-          else ptx::umma_commit_pair(empty_bar + 8u * stage, 3);
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          for (int mi = 0; mi < MI; mi++) issue(stage, mi, d_tmem, kb == kb_begin);
+          release_slot(stage);
+          advance();
         }
         if (!ok) break;
-        // wakes the epilogue of every CTA holding rows of this accumulator
-        if constexpr (CTA_GROUP == 1) ptx::umma_commit(tmem_full_bar + 8u * acc);
-        else ptx::umma_commit_pair(tmem_full_bar + 8u * acc, 3);
+        if (G > 0) {
+          // ---- tail, row block 0 then row block 1 ----
+          for (int i = 0; ok && i < G; i++) {
+            ok = bounded_wait(full_bar + 8u * slot_of(i), phase_of(i), wctx, WAIT_FULL, (uint32_t)slot_of(i));
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            issue(slot_of(i), 0, d_tmem, false);
+          }
+          if (!ok) break;
+          publish(set * MI);
+          for (int i = 0; i < G; i++) {
+            issue(stage, 1, d_tmem, false);
+            release_slot(stage);
+            advance();
+          }
+          publish(set * MI + 1);
+        } else {
+          for (int mi = 0; mi < MI; mi++) publish(set * MI + mi);
+        }
       }
       if (!ok || *abort_ptr) {
         // let every UMMA in flight retire before TMEM is released
@@ -339,71 +414,76 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   } else {
     // ===== epilogue (examples/kernels/gemm.ml:143-161) =====
-    const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-    const int ew = warp - 2;    // staging slot
-    const uint32_t stage_buf0 = staging_base + (uint32_t)ew * 8192u;
+    const int quad = warp & 3;         // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    const int ew = warp - 2;           // 0..7, staging slot
+    const int group = ew >> 2;         // 0 or 1
+    const int mi = MI == 2 ? group : 0;
+    const int ch_begin = MI == 2 ? 0 : group * CHUNKS_PER_GROUP;
+    const uint32_t buf = staging_base + (uint32_t)ew * 4096u;  // one 32x32 f32 sub-tile
+    const uint32_t row_addr = buf + (uint32_t)lane * 128u;
     const uint32_t tmem_empty_remote =
         CTA_GROUP == 2 ? ptx::map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
     int local_tile = 0;
-    uint32_t store_count = 0;
     bool ok = true;
     for (int w = cluster_id; ok && w < total_work; w += num_clusters, local_tile++) {
       const int t = w / p.splits, sp = w - t * p.splits;
-      const int acc = local_tile & 1;
-      const uint32_t acc_phase = (uint32_t)(local_tile >> 1) & 1u;
+      const int set = local_tile % SETS;
+      const uint32_t set_phase = (uint32_t)(local_tile / SETS) & 1u;
+      const int unit = set * MI + mi;
       int tm, tn;
       grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
-      const int c_row0 = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) +
-                         (int)cta_rank * BM_CTA + quad * 32;
-      const int c_col0 = tn * BN;
+      const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
+                        mi * 128 + quad * 32;
+      const int c_col0 = tn * BN + ch_begin * 32;
       // one lane waits (the wait can last a whole main loop); the rest of the
       // warp parks at the shuffle instead of polling the barrier
       uint32_t got = 0;
       if (lane == 0)
-        got = bounded_wait(tmem_full_bar + 8u * acc, acc_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w) ? 1u : 0u;
+        got = bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) {
         ok = false;
         break;
       }
       ptx::tc_fence_after_sync();
-      const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-#pragma unroll 1
-      for (int mi = 0; mi < MMA_M_COUNT; mi++) {
-#pragma unroll 1
-        for (int ch = 0; ch < BN / 32; ch++) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(t_lane + (uint32_t)(mi * BN + ch * 32), v);
-          ptx::tmem_ld_wait();
-          if (mi == MMA_M_COUNT - 1 && ch == BN / 32 - 1) {
-            // the accumulator is now in registers everywhere in this warp:
-            // hand it back to the issuer before finishing the stores
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tmem_empty_bar + 8u * acc);
-              else ptx::mbar_arrive_cluster(tmem_empty_remote + 8u * acc);
-            }
-          }
-          const uint32_t buf = stage_buf0 + (store_count & 1u) * 4096u;
-          // the store that last read this buffer must be done reading it
-          if (lane == 0) ptx::tma_store_wait_read<1>();
-          __syncwarp();
-          // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
-          // (row % 8) as the 128-byte-swizzle store map expects
-          const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                              (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
+      // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is
+      // in flight while chunk c goes through shared memory to the TMA store.
+      uint32_t va[32], vb[32];
+      ptx::tmem_ld_32x32b_x32(t_addr, va);
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
-            ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
-                              v[4 * j + 2], v[4 * j + 3]);
-          }
-          ptx::fence_proxy_async_smem();
+      for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
+        uint32_t(&cur)[32] = (c & 1) ? vb : va;
+        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+        ptx::tmem_ld_wait();
+        if (c + 1 < CHUNKS_PER_GROUP) {
+          ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
+        } else {
+          // the unit is in registers everywhere in this warp: hand it back to
+          // the issuer before finishing the stores
+          ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d(map_c, c_col0 + ch * 32, c_row0 + mi * 128, buf);
-            ptx::tma_store_commit();
+            if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tmem_empty_bar + 8u * unit);
+            else ptx::mbar_arrive_cluster(tmem_empty_remote + 8u * unit);
           }
-          store_count++;
+        }
+        // the previous store must be done reading the staging buffer
+        if (lane == 0) ptx::tma_store_wait_read<0>();
+        __syncwarp();
+        // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
+        // (row % 8) as the 128-byte-swizzle store map expects
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
+                            cur[4 * j + 2], cur[4 * j + 3]);
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(map_c, c_col0 + c * 32, c_row, buf);
+          ptx::tma_store_commit();
         }
       }
     }

@@ -15,20 +15,25 @@ import torch
 from . import catalog
 from ._lib import check, lib
 
-VARIANT_AUTO, V_1CTA_128x256, V_1CTA_128x128, V_1CTA_256x128, V_2CTA_256x256, V_2CTA_256x128, V_SPLITK = range(7)
+(VARIANT_AUTO, V_1CTA_128x256, V_1CTA_128x128, V_1CTA_256x128, V_2CTA_256x256, V_2CTA_256x128, V_SPLITK,
+ V_2CTA_512x256) = range(8)
 VARIANT_NAMES = {
     "auto": VARIANT_AUTO, "1cta_128x256": V_1CTA_128x256, "1cta_128x128": V_1CTA_128x128,
     "1cta_256x128": V_1CTA_256x128, "2cta_256x256": V_2CTA_256x256, "2cta_256x128": V_2CTA_256x128,
-    "splitk": V_SPLITK,
+    "splitk": V_SPLITK, "2cta_512x256": V_2CTA_512x256,
 }
 ELEMENT_BYTES = {"f32": 4, "bf16": 2}
 INPUT_NONE, INPUT_TF32, INPUT_BF16 = 0, 1, 2
 
 
-def make_flags(variant: int | str = VARIANT_AUTO, stages: int = 0, group_m: int = 0, splits: int = 0) -> int:
+def make_flags(variant: int | str = VARIANT_AUTO, stages: int = 0, group_m: int = 0, splits: int = 0,
+               reorder: int = 0) -> int:
+    """reorder: K blocks issued block-major at tile ends (256-row variants);
+    0 = library default, 15 = never."""
     if isinstance(variant, str):
         variant = VARIANT_NAMES[variant]
-    return (variant & 0xFF) | ((stages & 0xF) << 8) | ((group_m & 0xFF) << 12) | ((splits & 0xFF) << 20)
+    return ((variant & 0xFF) | ((stages & 0xF) << 8) | ((group_m & 0xFF) << 12) | ((splits & 0xFF) << 20) |
+            ((reorder & 0xF) << 28))
 
 
 def _stream(stream=None) -> int:

@@ -106,7 +106,7 @@ def test_parse_config(oxlib):
 def test_kernel_info_and_tiles(oxlib):
     for name in cat.ENTRY_NAMES:
         threads, dyn, total = cat.kernel_info(name)
-        assert threads == 192                       # 6 warps: TMA, UMMA, 4 epilogue
+        assert threads == 320                       # 10 warps: TMA, UMMA, 8 epilogue
         assert 118784 <= dyn <= 232448 and total == dyn
         tile, eb = cat.kernel_tile(name)
         assert eb == (2 if name == "gemm_bf16_fast" else 4)

@@ -31,7 +31,7 @@ from oxcamlgpu_b200._lib import OxgpuError
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
-TC_VARIANTS = ["1cta_128x256", "1cta_128x128", "1cta_256x128", "2cta_256x256", "2cta_256x128"]
+TC_VARIANTS = ["1cta_128x256", "1cta_128x128", "1cta_256x128", "2cta_256x256", "2cta_256x128", "2cta_512x256"]
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -227,6 +227,23 @@ def test_ring_and_parity_sweep_bf16(variant, kblocks):
         check_bf16(a_bits, bt_bits, c)
 
 
+@pytest.mark.parametrize("variant", ["1cta_256x128", "2cta_512x256"])
+@pytest.mark.parametrize("reorder", [15, 1, 2, 3])
+@pytest.mark.parametrize("kblocks", [1, 2, 3, 5, 6, 7, 12])
+def test_block_major_tile_ends(variant, reorder, kblocks):
+    """256-row variants issue the first/last K blocks of a tile block-major; every
+    setting must give the same result, with several tiles per CTA."""
+    rng = np.random.default_rng(kblocks * 7 + reorder)
+    m, n, k = 2048, 2560, 64 * kblocks
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    for stages in (2, 0):
+        c = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits),
+                           flags=gemm.make_flags(variant, stages=stages, reorder=reorder))
+        check_bf16(a_bits, bt_bits, c, rows=np.array([0, 127, 128, 255, 256, 1000, 2047], np.int32))
+        exact = gemm.gemm_exact(bf16_tensor(a_bits), bf16_tensor(bt_bits), gemm.INPUT_BF16)
+        assert float((c - exact).abs().max()) <= strict_tol(k, 6.0, 6.0)
+
+
 @pytest.mark.parametrize("variant", TC_VARIANTS)
 def test_many_tiles_per_cta_and_accumulator_reuse(variant):
     """More tiles than CTAs: both TMEM accumulators are reused several times."""
@@ -397,7 +414,7 @@ def test_bf16_8192_cubed():
     exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
     assert np.array_equal(exact[rows].cpu().numpy(), expect)
     assert float((c - exact).abs().max()) <= tol
-    for variant in ("1cta_128x256", "2cta_256x128"):
+    for variant in ("1cta_128x256", "2cta_256x256", "2cta_256x128"):
         cv = gemm.gemm_bf16(a, bt, flags=gemm.make_flags(variant))
         assert float((cv - exact).abs().max()) <= tol
 
