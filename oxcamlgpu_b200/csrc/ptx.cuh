@@ -111,6 +111,47 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void *
       : "memory");
 }
 
+// L2 eviction-priority policies for TMA copies (whole-access, fraction 1.0).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const void *map, int c0, int c1,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_dst), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const void *map, int c0, int c1,
+                                                      uint32_t bar_cluster_addr, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_dst), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(bar_cluster_addr), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const void *map, int c0, int c1, uint32_t smem_src,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
+      ::"l"((uint64_t)map), "r"(c0), "r"(c1), "r"(smem_src), "l"(policy)
+      : "memory");
+}
+
 // 2-D tile store shared -> global through the bulk-group mechanism.
 __device__ __forceinline__ void tma_store_2d(const void *map, int c0, int c1, uint32_t smem_src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"

@@ -70,6 +70,9 @@ struct GemmParams {
   // Tiles with two row blocks per CTA: how many K blocks at either end of a tile
   // are issued block-major (see the issuer); 0 = always interleaved.
   int reorder_kb;
+  // L2 eviction priority of the A loads, the B^T loads and the C stores:
+  // 0 = normal, 1 = evict first, 2 = evict last.
+  int hint_a, hint_b, hint_c;
   unsigned long long wait_budget_ns;
 };
 
@@ -231,6 +234,11 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
+      auto policy = [](int h) {
+        return h == 1 ? ptx::l2_policy_evict_first() : h == 2 ? ptx::l2_policy_evict_last()
+                                                               : ptx::l2_policy_evict_normal();
+      };
+      const uint64_t pol_a = policy(p.hint_a), pol_b = policy(p.hint_b);
       for (int w = cluster_id; ok && w < total_work; w += num_clusters) {
         const int t = w / p.splits, sp = w - t * p.splits;
         const int kb_begin = sp * p.kb_per_split;
@@ -251,18 +259,18 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t bar = full_bar + 8u * stage;
             ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
             for (int r = 0; r < BM_CTA; r += p.a_box_rows)
-              ptx::tma_load_2d(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar);
+              ptx::tma_load_2d_hint(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar, pol_a);
             for (int r = 0; r < B_ROWS; r += p.b_box_rows)
-              ptx::tma_load_2d(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar);
+              ptx::tma_load_2d_hint(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar, pol_b);
           } else {
             // Both CTAs credit the leader's barrier; the leader expects the
             // bytes of the whole pair.
             if (is_leader) ptx::mbar_arrive_expect_tx(full_bar + 8u * stage, 2u * STAGE_BYTES);
             const uint32_t bar = full_remote0 + 8u * stage;
             for (int r = 0; r < BM_CTA; r += p.a_box_rows)
-              ptx::tma_load_2d_pair(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar);
+              ptx::tma_load_2d_pair_hint(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar, pol_a);
             for (int r = 0; r < B_ROWS; r += p.b_box_rows)
-              ptx::tma_load_2d_pair(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar);
+              ptx::tma_load_2d_pair_hint(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar, pol_b);
           }
           issued++;
           if (++stage == stages) {
@@ -425,6 +433,8 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
         CTA_GROUP == 2 ? ptx::map_to_cta(tmem_empty_bar, 0) : tmem_empty_bar;
     int local_tile = 0;
     bool ok = true;
+    const uint64_t pol_c = p.hint_c == 1 ? ptx::l2_policy_evict_first()
+                           : p.hint_c == 2 ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_normal();
     for (int w = cluster_id; ok && w < total_work; w += num_clusters, local_tile++) {
       const int t = w / p.splits, sp = w - t * p.splits;
       const int set = local_tile % SETS;
@@ -482,7 +492,7 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_2d(map_c, c_col0 + c * 32, c_row, buf);
+          ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
           ptx::tma_store_commit();
         }
       }
