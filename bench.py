@@ -45,7 +45,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, from one ncu
 # capture of the same kernel (profiles/umma_gemm_bf16_8192.md); None = not captured.
-NCU_TRAFFIC_BYTES = {"bf16_8192": 1.519e9}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 1.085e9}
 
 
 def measured_peaks():
