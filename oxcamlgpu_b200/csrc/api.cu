@@ -390,9 +390,13 @@ int ensure_staging(Staging &s, size_t a_bytes, size_t bt_bytes, size_t c_bytes) 
   return OXGPU_OK;
 }
 
-// Host-buffer GEMM: B^T goes up once; A goes up, C is computed and comes down
-// in row blocks, with upload, compute and download on three streams so the two
-// copy directions and the math overlap.
+// Host-buffer GEMM.  PCIe is the limit (operands up, C down), so the schedule
+// keeps both directions busy: A and B^T go up in row blocks, alternating
+// A0 B0 A1 B1 ..., and as soon as a block lands the library computes every part
+// of C that has just become computable (a new block row of C against the B^T
+// blocks already present, or a new block column against the A blocks already
+// present) and starts its download.  Uploads, GEMMs and downloads run on three
+// streams chained by events.
 int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, int m, int n, int k,
               unsigned flags) {
   const int esize = kind == 0 ? 2 : 4;
@@ -409,31 +413,61 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
   const size_t c_bytes = (size_t)m * n * sizeof(float);
   if ((st = ensure_staging(s, a_bytes, bt_bytes, c_bytes))) return st;
 
-  // Row blocks: multiples of 256 rows, at most 64 blocks, about 8 per problem.
-  int block_rows = ((m / 8 + 255) / 256) * 256;
-  if (block_rows < 256) block_rows = 256;
-  while ((m + block_rows - 1) / block_rows > 64) block_rows *= 2;
-  const int blocks = (m + block_rows - 1) / block_rows;
+  // Row blocks: multiples of 256 rows, about 8 per operand, at most 16.
+  auto block_rows_of = [](int rows) {
+    int b = ((rows / 8 + 255) / 256) * 256;
+    if (b < 256) b = 256;
+    while ((rows + b - 1) / b > 16) b *= 2;
+    return b;
+  };
+  const int a_rows = block_rows_of(m), b_rows = block_rows_of(n);
+  const int na = (m + a_rows - 1) / a_rows, nb = (n + b_rows - 1) / b_rows;
+  const size_t row_bytes = (size_t)k * esize;
+  int a_up = 0, b_up = 0, ev = 0;  // blocks uploaded so far; next event slot
 
-  OX_CUDA(cudaMemcpyAsync(s.bt, bt_host, bt_bytes, cudaMemcpyHostToDevice, s.in));
-  OX_CUDA(cudaEventRecord(s.bt_ready, s.in));
-  OX_CUDA(cudaStreamWaitEvent(s.compute, s.bt_ready, 0));
-  for (int b = 0; b < blocks; b++) {
-    const int r0 = b * block_rows;
-    const int rows = m - r0 < block_rows ? m - r0 : block_rows;
-    const char *a_src = (const char *)a_host + (size_t)r0 * k * esize;
-    char *a_dst = (char *)s.a + (size_t)r0 * k * esize;
-    OX_CUDA(cudaMemcpyAsync(a_dst, a_src, (size_t)rows * k * esize, cudaMemcpyHostToDevice, s.in));
-    OX_CUDA(cudaEventRecord(s.a_ready[b], s.in));
-    OX_CUDA(cudaStreamWaitEvent(s.compute, s.a_ready[b], 0));
-    float *c_dst = (float *)s.c + (size_t)r0 * n;
-    if ((st = gemm_buffers(kind, a_dst, s.bt, c_dst, rows, n, k, k, k, n, flags, nullptr, 0,
-                           s.compute)))
-      return st;
-    OX_CUDA(cudaEventRecord(s.c_ready[b], s.compute));
-    OX_CUDA(cudaStreamWaitEvent(s.out, s.c_ready[b], 0));
-    OX_CUDA(cudaMemcpyAsync(c_host + (size_t)r0 * n, c_dst, (size_t)rows * n * sizeof(float),
-                            cudaMemcpyDeviceToHost, s.out));
+  // compute C[r0:r0+rows, c0:c0+cols] on the device and send it down
+  auto emit = [&](int r0, int rows, int c0, int cols, cudaEvent_t ready) -> int {
+    OX_CUDA(cudaStreamWaitEvent(s.compute, ready, 0));
+    const char *a_dev = (const char *)s.a + (size_t)r0 * row_bytes;
+    const char *b_dev = (const char *)s.bt + (size_t)c0 * row_bytes;
+    float *c_dev = (float *)s.c + (size_t)r0 * n + c0;
+    int st2 = gemm_buffers(kind, a_dev, b_dev, c_dev, rows, cols, k, k, k, n, flags, nullptr, 0, s.compute);
+    if (st2) return st2;
+    cudaEvent_t done = s.c_ready[ev % 64];
+    OX_CUDA(cudaEventRecord(done, s.compute));
+    OX_CUDA(cudaStreamWaitEvent(s.out, done, 0));
+    OX_CUDA(cudaMemcpy2DAsync(c_host + (size_t)r0 * n + c0, (size_t)n * sizeof(float), c_dev,
+                              (size_t)n * sizeof(float), (size_t)cols * sizeof(float), (size_t)rows,
+                              cudaMemcpyDeviceToHost, s.out));
+    return OXGPU_OK;
+  };
+
+  while (a_up < na || b_up < nb) {
+    // next upload: keep the two operands' progress balanced (as fractions)
+    const bool take_a = b_up >= nb || (a_up < na && (long long)a_up * nb <= (long long)b_up * na);
+    cudaEvent_t up = s.a_ready[ev % 64];
+    if (take_a) {
+      const int r0 = a_up * a_rows, rows = m - r0 < a_rows ? m - r0 : a_rows;
+      OX_CUDA(cudaMemcpyAsync((char *)s.a + (size_t)r0 * row_bytes, (const char *)a_host + (size_t)r0 * row_bytes,
+                              (size_t)rows * row_bytes, cudaMemcpyHostToDevice, s.in));
+      OX_CUDA(cudaEventRecord(up, s.in));
+      a_up++;
+      if (b_up > 0) {  // new block row of C against every B^T block present
+        const int cols = b_up * b_rows < n ? b_up * b_rows : n;
+        if ((st = emit(r0, rows, 0, cols, up))) return st;
+      }
+    } else {
+      const int c0 = b_up * b_rows, cols = n - c0 < b_rows ? n - c0 : b_rows;
+      OX_CUDA(cudaMemcpyAsync((char *)s.bt + (size_t)c0 * row_bytes, (const char *)bt_host + (size_t)c0 * row_bytes,
+                              (size_t)cols * row_bytes, cudaMemcpyHostToDevice, s.in));
+      OX_CUDA(cudaEventRecord(up, s.in));
+      b_up++;
+      if (a_up > 0) {  // new block column of C against every A block present
+        const int rows = a_up * a_rows < m ? a_up * a_rows : m;
+        if ((st = emit(0, rows, c0, cols, up))) return st;
+      }
+    }
+    ev++;
   }
   OX_CUDA(cudaStreamSynchronize(s.out));
   OX_CUDA(cudaStreamSynchronize(s.in));
