@@ -335,6 +335,13 @@ def main():
             cublas_f32_med = reduce_max(statistics.median(f32_ms))
         except Exception:
             cublas_f32_med = None
+    out16_med = None
+    if kind == "bf16":
+        # the same work as cuBLAS's bf16-C path: the library's bf16-output entry point
+        c16 = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        out16_ms = timed_steps(lambda: gemm.gemm_bf16_out16(a, bt, c16, flags=flags), args.steps, 3)
+        out16_med = reduce_max(statistics.median(out16_ms))
+        del c16
     sampler.__exit__()
     del c_ref
 
@@ -415,7 +422,9 @@ def main():
                        "ours_second_window_median_ms": ours2_med,
                        "ours_over_cublas_second_window": cublas_med / ours2_med,
                        "f32_out_median_ms": cublas_f32_med,
-                       "ours_over_cublas_f32_out": (cublas_f32_med / median_ms) if cublas_f32_med else None},
+                       "ours_over_cublas_f32_out": (cublas_f32_med / median_ms) if cublas_f32_med else None,
+                       "ours_bf16_out_median_ms": out16_med,
+                       "ours_bf16_out_over_cublas": (cublas_med / out16_med) if out16_med else None},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": sampler.summary(),
             "check": {"max_abs_err_sampled_rows": err, "tolerance": tol},

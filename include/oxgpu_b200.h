@@ -161,6 +161,14 @@ OXGPU_API int oxgpu_b200_gemm_bf16(const uint16_t *a, const uint16_t *bt, float 
                                    int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
                                    void *stream);
 
+/* bf16 inputs, bf16 OUTPUT (f32 accumulation in TMEM, one round-to-nearest-even
+ * at the store): the narrow-output epilogue the reference lists as future work
+ * (docs/roadmap.md:67-71).  c: bf16 bits [M,N], ldc a multiple of 8.  Variants:
+ * auto, 1CTA_128x256, 1CTA_128x128, 2CTA_256x256, 2CTA_512x256. */
+OXGPU_API int oxgpu_b200_gemm_bf16_out16(const uint16_t *a, const uint16_t *bt, uint16_t *c, int m,
+                                         int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                         unsigned flags, void *stream);
+
 /* Same, with caller-provided scratch for OXGPU_VARIANT_SPLITK (f32 partial
  * tiles).  workspace_bytes must be at least
  * oxgpu_b200_splitk_workspace_bytes(m, n, splits). */

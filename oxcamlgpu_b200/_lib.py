@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
                                   ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_gemm_bf16": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                   ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_gemm_bf16_out16": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
+                                        ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_splitk_workspace_bytes": ([c_int, c_int, c_int], sz),
         "oxgpu_b200_gemm_bf16_ws": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                      ctypes.c_uint, c_void_p, sz, c_void_p], c_int),

@@ -22,7 +22,7 @@ namespace oxgpu {
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kKinds = 2;     // 0 = bf16, 1 = tf32
+constexpr int kKinds = 3;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C
 constexpr int kVariants = 8;  // index by Variant value (1..5 and 7 used)
 
 std::atomic<uint64_t> g_launches{0};
@@ -127,8 +127,17 @@ int encode_2d(CUtensorMap *map, const void *ptr, int element_bytes, uint64_t dim
   return OXGPU_OK;
 }
 
-const void *kernel_for(int kind, int variant) {
+const void *kernel_for(int kind, int variant, bool out16 = false) {
 #define OX_K(K, BM, BN, CG) ((const void *)umma_gemm_kernel<K, BM, BN, CG>)
+  if (out16) {  // bf16 inputs, bf16 C
+    switch (variant) {
+      case VARIANT_1CTA_128x256: return (const void *)umma_gemm_kernel<0, 128, 256, 1, true>;
+      case VARIANT_1CTA_128x128: return (const void *)umma_gemm_kernel<0, 128, 128, 1, true>;
+      case VARIANT_2CTA_256x256: return (const void *)umma_gemm_kernel<0, 128, 256, 2, true>;
+      case VARIANT_2CTA_512x256: return (const void *)umma_gemm_kernel<0, 256, 256, 2, true>;
+    }
+    return nullptr;
+  }
   if (kind == 0) {
     switch (variant) {
       case VARIANT_1CTA_128x256: return OX_K(0, 128, 256, 1);
@@ -166,6 +175,7 @@ struct LaunchPlan {
   int kind, variant, stages, group_m;
   int splits, kb_per_split, split_row_stride;
   int reorder_kb = -1;  // -1: library default
+  bool out16 = false;   // bf16 C
 };
 
 // K blocks issued block-major at either end of a tile (two-row-block tiles).
@@ -176,7 +186,7 @@ constexpr int kDefaultReorderKb = 3;
 int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, int n, int k,
                 cudaStream_t stream) {
   const VariantShape shape = variant_shape(plan.variant);
-  const void *fn = kernel_for(plan.kind, plan.variant);
+  const void *fn = kernel_for(plan.kind, plan.variant, plan.out16);
   if (!fn || shape.cta_group == 0) return fail(OXGPU_E_INVALID_ARG, "unknown kernel variant");
   int stages = plan.stages;
   const int most = variant_max_stages(plan.variant);
@@ -206,7 +216,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   p.hint_c = 1;
   p.wait_budget_ns = wait_budget_ns();
 
-  bool &attr = dev.attr_set[plan.kind][plan.variant];
+  bool &attr = dev.attr_set[plan.out16 ? 2 : plan.kind][plan.variant];
   if (!attr) {
     OX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
     attr = true;
@@ -228,7 +238,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    int &maxc = dev.max_clusters[plan.kind][plan.variant];
+    int &maxc = dev.max_clusters[plan.out16 ? 2 : plan.kind][plan.variant];
     if (maxc == 0) {
       cfg.gridDim = dim3(2 * (dev.sm_count / 2), 1, 1);
       int nc = 0;
@@ -285,10 +295,11 @@ int choose_variant(const DeviceState &dev, int m, int n, int k) {
 
 int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
                  int64_t ldb, int64_t ldc, unsigned flags, void *workspace, size_t workspace_bytes,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, bool out16 = false) {
   const int esize = kind == 0 ? 2 : 4;
   int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, esize);
   if (st) return st;
+  if (out16 && (ldc * 2) % 16) return fail(OXGPU_E_ALIGN, "bf16 C needs ldc to be a multiple of 8");
   int dev_index;
   DeviceState *dev;
   if ((st = current_device(&dev_index, &dev))) return st;
@@ -298,8 +309,13 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   const int group_m = (int)((flags >> 12) & 0xffu);
   int splits = (int)((flags >> 20) & 0xffu);
   const bool splitk = variant == VARIANT_SPLITK;
-  if (variant == VARIANT_AUTO) variant = choose_variant(*dev, m, n, k);
+  const bool was_auto = variant == VARIANT_AUTO;
+  if (was_auto) variant = choose_variant(*dev, m, n, k);
   if (splitk) variant = VARIANT_1CTA_128x128;
+  if (out16 && !splitk && !kernel_for(0, variant, true)) {
+    if (!was_auto) return fail(OXGPU_E_INVALID_ARG, "this variant has no bf16-output kernel");
+    variant = VARIANT_1CTA_128x128;
+  }
   if (variant_shape(variant).cta_group == 0)
     return fail(OXGPU_E_INVALID_ARG, "unknown variant in flags");
   const VariantShape shape = variant_shape(variant);
@@ -318,6 +334,13 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   if ((st = encode_2d(&p.map_b, bt, esize, (uint64_t)k, (uint64_t)n, (uint64_t)ldb * esize, kbe, b_box)))
     return st;
 
+  if (out16) {
+    if (splitk) return fail(OXGPU_E_INVALID_ARG, "split-K writes f32 partial tiles; no bf16 output");
+    plan.out16 = true;
+    if ((st = encode_2d(&p.map_c, c, 2, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 2, 64, 32)))
+      return st;
+    return launch_umma(*dev, plan, p, m, n, k, stream);
+  }
   if (!splitk) {
     if ((st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32)))
       return st;
@@ -541,6 +564,16 @@ int oxgpu_b200_gemm_bf16(const uint16_t *a, const uint16_t *bt, float *c, int m,
   if ((flags & 0xffu) == VARIANT_SPLITK)
     return fail(OXGPU_E_INVALID_ARG, "split-K needs a workspace: use the _ws entry point");
   return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, nullptr, 0, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_bf16_out16(const uint16_t *a, const uint16_t *bt, uint16_t *c, int m, int n, int k,
+                               int64_t lda, int64_t ldb, int64_t ldc, unsigned flags, void *stream) {
+  // check_buffers treats C as 4-byte elements for alignment; bf16 C is checked inside
+  unsigned v = flags & 0xffu;
+  if (v == VARIANT_1CTA_256x128 || v == VARIANT_2CTA_256x128 || v == VARIANT_SPLITK)
+    return fail(OXGPU_E_INVALID_ARG, "this variant has no bf16-output kernel");
+  return gemm_buffers(0, a, bt, (float *)c, m, n, k, lda, ldb, ldc, flags, nullptr, 0, (cudaStream_t)stream,
+                      true);
 }
 
 size_t oxgpu_b200_splitk_workspace_bytes(int m, int n, int splits) {

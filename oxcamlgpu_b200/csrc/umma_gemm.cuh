@@ -131,7 +131,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
          ((uint32_t)(umma_m >> 4) << 24);
 }
 
-template <int KIND, int BM_CTA, int BN, int CTA_GROUP>
+// OUT16: C is stored as bf16 (round to nearest even) instead of f32 -- the
+// narrow-output epilogue the reference lists as future work
+// (docs/roadmap.md:67-71); the C map is then a bf16 map with 64-column boxes.
+template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
 umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   // A CTA owns BM_CTA rows of the tile as MI blocks of 128 rows (one UMMA each
@@ -458,42 +461,71 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       ptx::tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                               (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
-      // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is
-      // in flight while chunk c goes through shared memory to the TMA store.
-      uint32_t va[32], vb[32];
-      ptx::tmem_ld_32x32b_x32(t_addr, va);
-#pragma unroll
-      for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
-        uint32_t(&cur)[32] = (c & 1) ? vb : va;
-        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-        ptx::tmem_ld_wait();
-        if (c + 1 < CHUNKS_PER_GROUP) {
-          ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
-        } else {
-          // the unit is in registers everywhere in this warp: hand it back to
-          // the issuer before finishing the stores
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tmem_empty_bar + 8u * unit);
-            else ptx::mbar_arrive_cluster(tmem_empty_remote + 8u * unit);
-          }
-        }
-        // the previous store must be done reading the staging buffer
-        if (lane == 0) ptx::tma_store_wait_read<0>();
-        __syncwarp();
-        // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
-        // (row % 8) as the 128-byte-swizzle store map expects
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
-                            cur[4 * j + 2], cur[4 * j + 3]);
-        }
-        ptx::fence_proxy_async_smem();
+      auto release_unit = [&]() {
+        // the unit is in registers everywhere in this warp: hand it back to
+        // the issuer before finishing the stores
+        ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
-          ptx::tma_store_commit();
+          if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tmem_empty_bar + 8u * unit);
+          else ptx::mbar_arrive_cluster(tmem_empty_remote + 8u * unit);
+        }
+      };
+      if constexpr (!OUT16) {
+        // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is
+        // in flight while chunk c goes through shared memory to the TMA store.
+        uint32_t va[32], vb[32];
+        ptx::tmem_ld_32x32b_x32(t_addr, va);
+#pragma unroll
+        for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
+          uint32_t(&cur)[32] = (c & 1) ? vb : va;
+          uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+          ptx::tmem_ld_wait();
+          if (c + 1 < CHUNKS_PER_GROUP) ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
+          else release_unit();
+          // the previous store must be done reading the staging buffer
+          if (lane == 0) ptx::tma_store_wait_read<0>();
+          __syncwarp();
+          // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
+          // (row % 8) as the 128-byte-swizzle store map expects
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
+                              cur[4 * j + 2], cur[4 * j + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
+            ptx::tma_store_commit();
+          }
+        }
+      } else {
+        // bf16 C: two 32-column chunks make one 128-byte row of 64 bf16.
+        static_assert(CHUNKS_PER_GROUP % 2 == 0, "bf16 output needs column chunks in pairs");
+#pragma unroll 1
+        for (int c2 = 0; c2 < CHUNKS_PER_GROUP / 2; c2++) {
+          uint32_t va[32], vb[32];
+          ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c2 * 64), va);
+          ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c2 * 64 + 32), vb);
+          ptx::tmem_ld_wait();
+          if (c2 + 1 == CHUNKS_PER_GROUP / 2) release_unit();
+          if (lane == 0) ptx::tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            uint32_t(&src)[32] = j < 4 ? va : vb;
+            const int o = (j & 3) * 8;
+            ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4),
+                              ptx::pack_bf16x2(src[o], src[o + 1]), ptx::pack_bf16x2(src[o + 2], src[o + 3]),
+                              ptx::pack_bf16x2(src[o + 4], src[o + 5]), ptx::pack_bf16x2(src[o + 6], src[o + 7]));
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d_hint(map_c, c_col0 + c2 * 64, c_row, buf, pol_c);
+            ptx::tma_store_commit();
+          }
         }
       }
     }

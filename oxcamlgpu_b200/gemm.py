@@ -134,6 +134,21 @@ def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, 
     return c
 
 
+def gemm_bf16_out16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
+                    stream=None) -> torch.Tensor:
+    """bf16 A[M,K], B^T[N,K] -> bf16 C[M,N] (f32 accumulation, one RNE rounding at
+    the store): the narrow-output epilogue of docs/roadmap.md:67-71."""
+    m, n, k = _check_operands(a, bt, torch.bfloat16)
+    if c is None:
+        c = torch.empty(m, n, device=a.device, dtype=torch.bfloat16)
+    if c.dtype != torch.bfloat16 or c.stride(1) != 1 or tuple(c.shape) != (m, n):
+        raise ValueError("C must be bf16 [M,N] with unit column stride")
+    check(lib().oxgpu_b200_gemm_bf16_out16(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0),
+                                           bt.stride(0), c.stride(0), flags,
+                                           ctypes.c_void_p(_stream(stream))))
+    return c
+
+
 STATIC_SCRATCH_BYTES = 32 << 20
 
 

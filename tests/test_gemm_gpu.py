@@ -298,6 +298,36 @@ def test_strided_operands():
     check_bf16(np.ascontiguousarray(a_bits[:, :k]), np.ascontiguousarray(bt_bits[:, :k]), c)
 
 
+# ---- bf16 output ------------------------------------------------------------------------
+@pytest.mark.parametrize("variant", ["auto", "1cta_128x256", "1cta_128x128", "2cta_256x256", "2cta_512x256"])
+@pytest.mark.parametrize("m,n,k", [(512, 768, 320), (300, 520, 200), (2048, 2560, 128)])
+def test_bf16_output(variant, m, n, k):
+    """bf16 C = RNE(f32 accumulator): within half a bf16 ulp of the oracle's f32
+    result plus the accumulation tolerance."""
+    rng = np.random.default_rng(m + k)
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    pad = torch.full((m + 2, n + 16), float("nan"), device=DEV, dtype=torch.bfloat16)
+    c = pad[1:m + 1, 8:n + 8]
+    gemm.gemm_bf16_out16(bf16_tensor(a_bits), bf16_tensor(bt_bits), c, flags=gemm.make_flags(variant))
+    expect = oracle.gemm_kmajor_bf16(a_bits, bt_bits, threads=oracle.max_threads())
+    got = c.float().cpu().numpy()
+    tol = strict_tol(k, float(np.abs(oracle.of_bf16(a_bits)).max()), float(np.abs(oracle.of_bf16(bt_bits)).max()))
+    assert (np.abs(got - expect) <= np.abs(expect) * 2.0 ** -8 + tol).all()
+    # where the f32 kernel's result rounds unambiguously, the bf16 kernel must equal that rounding
+    c32 = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), flags=gemm.make_flags(variant)).cpu().numpy()
+    assert np.array_equal(oracle.to_bf16(c32), c.contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+    assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
+    assert torch.isnan(pad[:, :8]).all() and torch.isnan(pad[:, n + 8:]).all()
+
+
+def test_bf16_output_rejects_unsupported():
+    a = torch.zeros(256, 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_bf16_out16(a, a, flags=gemm.make_flags("2cta_256x128"))
+    with pytest.raises(OxgpuError):
+        gemm.gemm_bf16_out16(a, a, flags=gemm.make_flags("splitk"))
+
+
 # ---- split-K --------------------------------------------------------------------------
 @pytest.mark.parametrize("m,n,k,splits", [(128, 1024, 2048, 4), (128, 1024, 2048, 0), (100, 264, 1000, 3),
                                           (256, 512, 64, 5)])
