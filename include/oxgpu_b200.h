@@ -96,6 +96,47 @@ OXGPU_API int oxgpu_b200_kernel_info(const char *name, int *threads, int *dynami
  * (examples/kernels/gemm.ml:165-199): element_bytes 4 = f32/TF32, 2 = bf16. */
 OXGPU_API int oxgpu_b200_kernel_tile(const char *name, oxgpu_tile_config *tile, int *element_bytes);
 
+/* ---- `.gpu` kernel metadata: lib/frontend/gpu_metadata.ml (format 3) -------
+ * The adapter writes one tab-separated text file per kernel; its header names
+ * the kernel, its CTA width and the type and modes of every argument.  Reading
+ * that header lets a caller check that the `.gpu` file it holds describes the
+ * catalog entry it is about to launch through this library. */
+enum {
+  OXGPU_TY_SCALAR_I32 = 1, OXGPU_TY_SCALAR_F32, OXGPU_TY_BOOL, OXGPU_TY_UNIT, OXGPU_TY_BUFFER_F32,
+  OXGPU_TY_BUFFER_BF16, OXGPU_TY_BUFFER_F16, OXGPU_TY_TENSOR_MAP, OXGPU_TY_SCALAR_U64
+};
+enum { OXGPU_OWN_UNIQUE = 1, OXGPU_OWN_ALIASED };
+enum { OXGPU_LOC_LOCAL = 1, OXGPU_LOC_GLOBAL };
+enum { OXGPU_PORT_PORTABLE = 1, OXGPU_PORT_NONPORTABLE, OXGPU_PORT_UNSPECIFIED };
+enum { OXGPU_PERM_READ = 1, OXGPU_PERM_WRITE, OXGPU_PERM_READ_WRITE, OXGPU_PERM_IMMUTABLE };
+
+typedef struct oxgpu_gpu_slot { /* Kernel_ast slot as encoded by `slot` (gpu_metadata.ml:112-128) */
+  int type, ownership, locality, portability, permission;
+  int start_line, start_col, end_line, end_col;
+} oxgpu_gpu_slot;
+
+typedef struct oxgpu_gpu_header {
+  char kernel[64];
+  int threads;   /* 0 when the file has no `threads` row */
+  int nargs;
+  oxgpu_gpu_slot args[16];
+  oxgpu_gpu_slot result;
+} oxgpu_gpu_header;
+
+/* The header part of `parse` (lib/frontend/gpu_metadata.ml:289-343): rows
+ * `format 3`, `kernel NAME`, optional `threads N` (1..1024), `arg I <slot>` with
+ * contiguous ids, `result <slot>`; the instruction rows that follow are not
+ * read.  Failures return OXGPU_E_CONFIG with the reference's Parse_error text. */
+OXGPU_API int oxgpu_b200_parse_gpu_header(const char *text, size_t length, oxgpu_gpu_header *out);
+
+/* Does this header describe a GEMM catalog entry this library serves?  The
+ * kernel name must be one of the ten entry symbols, `threads` must be the
+ * entry's Hopper CTA width 128*(bm/64)+32 (examples/kernels/gemm.ml:165-199),
+ * and the arguments must be the entry point's: two tensor maps (aliased, read),
+ * a f32 buffer (unique, read_write) and three i32 scalars (gemm.ml:50-53).
+ * OXGPU_E_UNKNOWN_KERNEL / OXGPU_E_CONFIG say what does not match. */
+OXGPU_API int oxgpu_b200_check_gpu_header(const oxgpu_gpu_header *header);
+
 /* Gpu.grouped_tile_m / grouped_tile_n (tools/exporter/export_prims_index.ml:
  * 40-61; used at examples/kernels/gemm.ml:73-75): the grouped CTA order as a
  * pure function of the linear tile id, the one the persistent scheduler uses. */

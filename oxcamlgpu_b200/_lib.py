@@ -20,6 +20,16 @@ class OxgpuError(RuntimeError):
         self.message = message
 
 
+class GpuSlotStruct(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("type", "ownership", "locality", "portability", "permission",
+                                            "start_line", "start_col", "end_line", "end_col")]
+
+
+class GpuHeaderStruct(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_char * 64), ("threads", ctypes.c_int), ("nargs", ctypes.c_int),
+                ("args", GpuSlotStruct * 16), ("result", GpuSlotStruct)]
+
+
 class TileConfigStruct(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("bm", "bn", "bk", "stages", "producers")]
 
@@ -51,6 +61,8 @@ def lib() -> ctypes.CDLL:
         "oxgpu_b200_choose_config": ([c_int, c_int, c_int, cfgp], c_int),
         "oxgpu_b200_kernel_info": ([c_char_p, intp, intp, intp], c_int),
         "oxgpu_b200_kernel_tile": ([c_char_p, cfgp, intp], c_int),
+        "oxgpu_b200_parse_gpu_header": ([c_char_p, sz, ctypes.POINTER(GpuHeaderStruct)], c_int),
+        "oxgpu_b200_check_gpu_header": ([ctypes.POINTER(GpuHeaderStruct)], c_int),
         "oxgpu_b200_grouped_tile": ([c_int, c_int, c_int, c_int, intp, intp], c_int),
         "oxgpu_b200_encode_tmap_2d": ([c_void_p, c_void_p, c_int, u64, u64, u64, u32, u32], c_int),
         "oxgpu_b200_gemm_tmap": ([c_char_p, u64, u64, u64, c_int, c_int, c_int, c_void_p], c_int),

@@ -150,6 +150,46 @@ def grouped_tile(pid: int, group: int, tiles_m: int, tiles_n: int) -> tuple[int,
     return tm.value, tn.value
 
 
+TYPE_NAMES = {1: "scalar_i32", 2: "scalar_f32", 3: "bool", 4: "unit", 5: "buffer_f32", 6: "buffer_bf16",
+              7: "buffer_f16", 8: "tensor_map", 9: "scalar_u64"}
+OWNERSHIP_NAMES = {1: "unique", 2: "aliased"}
+PERMISSION_NAMES = {1: "read", 2: "write", 3: "read_write", 4: "immutable"}
+
+
+@dataclass(frozen=True)
+class GpuArg:
+    type: str
+    ownership: str
+    permission: str
+
+
+@dataclass(frozen=True)
+class GpuHeader:
+    """Header of a `.gpu` metadata file (lib/frontend/gpu_metadata.ml, format 3)."""
+    kernel: str
+    threads: int | None
+    args: tuple
+    _raw: object = None
+
+
+def parse_gpu_header(text: str) -> GpuHeader:
+    """The header part of Gpu_metadata.parse (gpu_metadata.ml:289-343); raises
+    ValueError with the reference's Parse_error text."""
+    from ._lib import GpuHeaderStruct
+    raw = GpuHeaderStruct()
+    data = text.encode()
+    _invalid(lib().oxgpu_b200_parse_gpu_header, data, len(data), ctypes.byref(raw))
+    args = tuple(GpuArg(TYPE_NAMES[a.type], OWNERSHIP_NAMES[a.ownership], PERMISSION_NAMES[a.permission])
+                 for a in list(raw.args)[:raw.nargs])
+    return GpuHeader(raw.kernel.decode(), raw.threads or None, args, raw)
+
+
+def check_gpu_header(header: GpuHeader) -> None:
+    """Raises ValueError unless the header describes a GEMM catalog entry this
+    library serves (name, CTA width, argument types and modes)."""
+    _invalid(lib().oxgpu_b200_check_gpu_header, ctypes.byref(header._raw))
+
+
 ENTRY_NAMES = (
     "gemm_fast", "gemm_bm128_bn256_s3", "gemm_bm128_bn256_s2", "gemm_bm128_bn128_s3",
     "gemm_bm128_bn128_s2", "gemm_bm64_bn256_s3", "gemm_bm64_bn256_s2", "gemm_bm256_bn128_s3",

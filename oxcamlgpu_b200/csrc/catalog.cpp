@@ -6,6 +6,7 @@
 #include <cstring>
 #include <map>
 #include <string>
+#include <vector>
 
 #include "common.hpp"
 
@@ -167,6 +168,113 @@ static int parse_config(const char *spec, oxgpu_tile_config *out) {
   return OXGPU_OK;
 }
 
+// ---- .gpu metadata header (lib/frontend/gpu_metadata.ml, format 3) ---------------
+static std::vector<std::string> split(const std::string &s, char sep) {
+  std::vector<std::string> out;
+  size_t start = 0;
+  while (true) {
+    size_t pos = s.find(sep, start);
+    out.push_back(s.substr(start, pos == std::string::npos ? std::string::npos : pos - start));
+    if (pos == std::string::npos) break;
+    start = pos + 1;
+  }
+  return out;
+}
+
+// `integer` / `id` (gpu_metadata.ml:12-18)
+static int meta_integer(const std::string &text, int *v) {
+  if (!parse_ocaml_int(text, v)) return fail(OXGPU_E_CONFIG, "invalid integer " + text);
+  return OXGPU_OK;
+}
+static int meta_id(const std::string &text, int *v) {
+  int st = meta_integer(text, v);
+  if (st) return st;
+  if (*v < 0) return fail(OXGPU_E_CONFIG, "negative value/argument id");
+  return OXGPU_OK;
+}
+
+// `parse_slot` (gpu_metadata.ml:130-159): type, ownership, locality,
+// portability, permission, then the source span (quoted file, four numbers).
+static int parse_slot(const std::vector<std::string> &f, size_t from, oxgpu_gpu_slot *out) {
+  if (f.size() - from != 10) return fail(OXGPU_E_CONFIG, "missing or extra mode fields");
+  const std::string &file = f[from + 5];
+  if (file.size() < 2 || file.front() != '"' || file.back() != '"')
+    return fail(OXGPU_E_CONFIG, "invalid source filename");
+  int st;
+  if ((st = meta_id(f[from + 6], &out->start_line)) || (st = meta_id(f[from + 7], &out->start_col)) ||
+      (st = meta_id(f[from + 8], &out->end_line)) || (st = meta_id(f[from + 9], &out->end_col)))
+    return st;
+  static const char *types[] = {"scalar_i32", "scalar_f32", "bool", "unit", "buffer_f32",
+                                "buffer_bf16", "buffer_f16", "tensor_map", "scalar_u64"};
+  out->type = 0;
+  for (int i = 0; i < 9; i++)
+    if (f[from] == types[i]) out->type = i + 1;
+  if (!out->type) return fail(OXGPU_E_CONFIG, "unsupported frontend type");
+  const std::string &o = f[from + 1], &l = f[from + 2], &p = f[from + 3], &a = f[from + 4];
+  out->ownership = o == "unique" ? OXGPU_OWN_UNIQUE : o == "aliased" ? OXGPU_OWN_ALIASED : 0;
+  if (!out->ownership) return fail(OXGPU_E_CONFIG, "invalid ownership");
+  out->locality = l == "local" ? OXGPU_LOC_LOCAL : l == "global" ? OXGPU_LOC_GLOBAL : 0;
+  if (!out->locality) return fail(OXGPU_E_CONFIG, "invalid locality");
+  out->portability = p == "portable" ? OXGPU_PORT_PORTABLE : p == "nonportable" ? OXGPU_PORT_NONPORTABLE
+                     : p == "unspecified" ? OXGPU_PORT_UNSPECIFIED : 0;
+  if (!out->portability) return fail(OXGPU_E_CONFIG, "invalid portability");
+  out->permission = a == "read" ? OXGPU_PERM_READ : a == "write" ? OXGPU_PERM_WRITE
+                    : a == "read_write" ? OXGPU_PERM_READ_WRITE : a == "immutable" ? OXGPU_PERM_IMMUTABLE : 0;
+  if (!out->permission) return fail(OXGPU_E_CONFIG, "invalid permission");
+  return OXGPU_OK;
+}
+
+// header part of `parse` (gpu_metadata.ml:289-343)
+static int parse_gpu_header(const std::string &source, oxgpu_gpu_header *out) {
+  std::vector<std::string> lines;
+  for (auto &line : split(source, '\n'))
+    if (!line.empty()) lines.push_back(line);  // blank lines are dropped before parsing
+  size_t pos = 0;
+  auto peek = [&]() { return pos == lines.size() ? std::vector<std::string>() : split(lines[pos], '\t'); };
+  std::memset(out, 0, sizeof *out);
+  {
+    auto row = peek();
+    pos++;
+    if (row.size() != 2 || row[0] != "format" || row[1] != "3")
+      return fail(OXGPU_E_CONFIG, "malformed region/header");
+  }
+  {
+    auto row = peek();
+    pos++;
+    if (row.size() != 2 || row[0] != "kernel" || row[1].empty()) return fail(OXGPU_E_CONFIG, "missing kernel");
+    if (row[1].size() >= sizeof out->kernel) return fail(OXGPU_E_TOO_LARGE, "kernel name too long");
+    std::strcpy(out->kernel, row[1].c_str());
+  }
+  {
+    auto row = peek();
+    if (row.size() == 2 && row[0] == "threads") {
+      pos++;
+      int st = meta_integer(row[1], &out->threads);
+      if (st) return st;
+      if (out->threads < 1 || out->threads > 1024)
+        return fail(OXGPU_E_CONFIG, "CTA thread count must be in 1..1024");
+    }
+  }
+  while (true) {
+    auto row = peek();
+    if (row.size() < 2 || row[0] != "arg") break;
+    pos++;
+    int index, st;
+    if ((st = meta_id(row[1], &index))) return st;
+    if (index != out->nargs) return fail(OXGPU_E_CONFIG, "argument ids must be contiguous");
+    if (out->nargs >= 16) return fail(OXGPU_E_TOO_LARGE, "more than 16 kernel arguments");
+    if ((st = parse_slot(row, 2, &out->args[out->nargs]))) return st;
+    out->nargs++;
+  }
+  {
+    auto row = peek();
+    if (row.empty() || row[0] != "result") return fail(OXGPU_E_CONFIG, "missing result");
+    int st = parse_slot(row, 1, &out->result);
+    if (st) return st;
+  }
+  return OXGPU_OK;
+}
+
 }  // namespace oxgpu
 
 using namespace oxgpu;
@@ -272,6 +380,37 @@ int oxgpu_b200_kernel_info(const char *name, int *threads, int *dynamic_smem, in
   if (threads) *threads = kThreadsPerCta;
   if (dynamic_smem) *dynamic_smem = smem;
   if (total_smem) *total_smem = smem;
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_parse_gpu_header(const char *text, size_t length, oxgpu_gpu_header *out) {
+  if (!text || !out) return fail(OXGPU_E_INVALID_ARG, "null argument");
+  return parse_gpu_header(std::string(text, length), out);
+}
+
+int oxgpu_b200_check_gpu_header(const oxgpu_gpu_header *h) {
+  if (!h) return fail(OXGPU_E_INVALID_ARG, "null argument");
+  const CatalogEntry *e = find_entry(h->kernel);
+  if (!e) return fail(OXGPU_E_UNKNOWN_KERNEL, std::string("no kernel named ") + h->kernel);
+  const int want_threads = threads_of(e->tile);
+  if (h->threads != want_threads) {
+    char text[160];
+    std::snprintf(text, sizeof text, "%s is specialised for %d threads per CTA, the metadata says %d",
+                  h->kernel, want_threads, h->threads);
+    return fail(OXGPU_E_CONFIG, text);
+  }
+  if (h->nargs != 6) return fail(OXGPU_E_CONFIG, "a GEMM entry point takes six arguments (a_tmap, b_tmap, c, m, n, k)");
+  for (int i = 0; i < 2; i++) {
+    const oxgpu_gpu_slot &s = h->args[i];
+    if (s.type != OXGPU_TY_TENSOR_MAP || s.ownership != OXGPU_OWN_ALIASED || s.permission != OXGPU_PERM_READ)
+      return fail(OXGPU_E_CONFIG, "arguments 0 and 1 must be tensor maps, aliased and read-only");
+  }
+  const oxgpu_gpu_slot &c = h->args[2];
+  if (c.type != OXGPU_TY_BUFFER_F32 || c.ownership != OXGPU_OWN_UNIQUE || c.permission != OXGPU_PERM_READ_WRITE)
+    return fail(OXGPU_E_CONFIG, "argument 2 must be the f32 output buffer, unique and read_write");
+  for (int i = 3; i < 6; i++)
+    if (h->args[i].type != OXGPU_TY_SCALAR_I32)
+      return fail(OXGPU_E_CONFIG, "arguments 3 to 5 must be i32 scalars (m, n, k)");
   return OXGPU_OK;
 }
 

@@ -142,3 +142,95 @@ def test_grouped_tile_is_a_bijection(oxlib, tiles_m, tiles_n, group):
             [(i, 0) for i in range(group)] + [(0, 1)]
     with pytest.raises(ValueError):
         cat.grouped_tile(tiles_m * tiles_n, group, tiles_m, tiles_n)
+
+
+# ---- .gpu metadata header (lib/frontend/gpu_metadata.ml, format 3) -----------------
+def _gpu_text(kernel="gemm_fast", threads=288, args=None, fmt="3", result=True, body=True):
+    span = '"examples/kernels/gemm.ml"\t50\t6\t50\t12'
+    if args is None:
+        args = [("tensor_map", "aliased", "global", "nonportable", "read"),
+                ("tensor_map", "aliased", "global", "nonportable", "read"),
+                ("buffer_f32", "unique", "global", "nonportable", "read_write"),
+                ("scalar_i32", "aliased", "global", "portable", "read"),
+                ("scalar_i32", "aliased", "global", "portable", "read"),
+                ("scalar_i32", "aliased", "global", "portable", "read")]
+    rows = [f"format\t{fmt}", f"kernel\t{kernel}"]
+    if threads is not None:
+        rows.append(f"threads\t{threads}")
+    for i, a in enumerate(args):
+        rows.append("\t".join(["arg", str(i), *a, span]))
+    if result:
+        rows.append("\t".join(["result", "unit", "aliased", "global", "portable", "read", span]))
+    if body:
+        rows += ['loc\t"examples/kernels/gemm.ml"\t54\t4\t54\t60', "body\tconst_i32\t0\t128", "yield\t-"]
+    return "\n".join(rows) + "\n"
+
+
+def test_gpu_header_round_trip_and_check(oxlib):
+    h = cat.parse_gpu_header(_gpu_text())
+    assert h.kernel == "gemm_fast" and h.threads == 288 and len(h.args) == 6
+    assert h.args[0] == cat.GpuArg("tensor_map", "aliased", "read")
+    assert h.args[2] == cat.GpuArg("buffer_f32", "unique", "read_write")
+    assert h.args[5].type == "scalar_i32"
+    cat.check_gpu_header(h)
+    # every f32 entry with its Hopper CTA width (gemm.ml:165-199)
+    for name in cat.ENTRY_NAMES:
+        tile, _ = cat.kernel_tile(name)
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(kernel=name, threads=128 * (tile.bm // 64) + 32)))
+    # blank lines are dropped, a file without `threads` parses
+    assert cat.parse_gpu_header("\n" + _gpu_text(threads=None)).threads is None
+
+
+@pytest.mark.parametrize("text,msg", [
+    (_gpu_text(fmt="2"), "malformed region/header"),
+    ("kernel\tgemm_fast\n", "malformed region/header"),
+    ("format\t3\nthreads\t288\n", "missing kernel"),
+    (_gpu_text(threads=0), "CTA thread count must be in 1..1024"),
+    (_gpu_text(threads=2048), "CTA thread count must be in 1..1024"),
+    (_gpu_text(threads="many"), "invalid integer many"),
+    (_gpu_text(result=False, body=False), "missing result"),
+    (_gpu_text(args=[("tensor_map", "shared", "global", "nonportable", "read")]), "invalid ownership"),
+    (_gpu_text(args=[("tensor_map", "aliased", "global", "nonportable", "execute")]), "invalid permission"),
+    (_gpu_text(args=[("tensor_map", "aliased", "remote", "nonportable", "read")]), "invalid locality"),
+    (_gpu_text(args=[("matrix", "aliased", "global", "nonportable", "read")]), "unsupported frontend type"),
+    (_gpu_text(args=[("tensor_map", "aliased", "global", "nonportable")]), "missing or extra mode fields"),
+])
+def test_gpu_header_parse_errors(oxlib, text, msg):
+    with pytest.raises(ValueError, match=msg):
+        cat.parse_gpu_header(text)
+
+
+def test_gpu_header_noncontiguous_args(oxlib):
+    text = _gpu_text().replace("arg\t1\t", "arg\t4\t", 1)
+    with pytest.raises(ValueError, match="argument ids must be contiguous"):
+        cat.parse_gpu_header(text)
+
+
+def test_gpu_header_check_rejections(oxlib):
+    with pytest.raises(ValueError, match="no kernel named saxpy"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(kernel="saxpy")))
+    with pytest.raises(ValueError, match="specialised for 288 threads per CTA, the metadata says 160"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(threads=160)))
+    with pytest.raises(ValueError, match="specialised for 160 threads"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(kernel="gemm_bm64_bn256_s3", threads=288)))
+    saxpy_args = [("buffer_f32", "aliased", "global", "nonportable", "read"),
+                  ("buffer_f32", "unique", "global", "nonportable", "read_write")]
+    with pytest.raises(ValueError, match="six arguments"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(args=saxpy_args)))
+    bad = [("tensor_map", "unique", "global", "nonportable", "read")] + [None] * 5
+    full = cat.parse_gpu_header(_gpu_text())
+    args = [("tensor_map", "unique", "global", "nonportable", "read"),
+            ("tensor_map", "aliased", "global", "nonportable", "read"),
+            ("buffer_f32", "unique", "global", "nonportable", "read_write")] + \
+           [("scalar_i32", "aliased", "global", "portable", "read")] * 3
+    with pytest.raises(ValueError, match="tensor maps, aliased and read-only"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(args=args)))
+    args[0] = ("tensor_map", "aliased", "global", "nonportable", "read")
+    args[2] = ("buffer_f32", "aliased", "global", "nonportable", "read_write")
+    with pytest.raises(ValueError, match="unique and read_write"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(args=args)))
+    args[2] = ("buffer_f32", "unique", "global", "nonportable", "read_write")
+    args[4] = ("scalar_f32", "aliased", "global", "portable", "read")
+    with pytest.raises(ValueError, match="i32 scalars"):
+        cat.check_gpu_header(cat.parse_gpu_header(_gpu_text(args=args)))
+    del bad, full

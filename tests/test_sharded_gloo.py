@@ -101,3 +101,43 @@ def test_two_ranks_gloo_shard_gather_reassemble():
         msgs.append(failures.get())
     assert not msgs, msgs
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def _failing_worker(rank, world, port, results):
+    """Rank 1 fails on the host before the exchange step; rank 0 must get an error
+    from the gather (short process-group timeout), not hang."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    dist.barrier()
+    if rank == 1:
+        results.put((rank, "failed before the gather"))
+        results.close()
+        results.join_thread()
+        os._exit(3)                      # the rank is gone: no kernels, no collectives in flight
+    try:
+        sharded.all_gather_c(torch.ones(4, 8))
+        results.put((rank, "gather returned"))
+    except Exception as e:               # noqa: BLE001 - any transport / timeout error is the expected outcome
+        results.put((rank, "error: " + type(e).__name__))
+    results.close()
+    results.join_thread()
+    os._exit(0)
+
+
+def test_rank_failure_surfaces_as_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert all(not p.is_alive() for p in procs), "a rank hung"
+    got = {}
+    while not results.empty():
+        r, msg = results.get()
+        got[r] = msg
+    assert got.get(1) == "failed before the gather" and procs[1].exitcode == 3
+    assert got.get(0, "").startswith("error: ") and procs[0].exitcode == 0
