@@ -177,7 +177,8 @@ enum {
   OXGPU_VARIANT_2CTA_256x256 = 4, /* CTA pair, cta_group::2 UMMA 256x256 */
   OXGPU_VARIANT_2CTA_256x128 = 5,
   OXGPU_VARIANT_SPLITK = 6,       /* 1-CTA 128x128 tiles over K slices + reduce; needs workspace */
-  OXGPU_VARIANT_2CTA_512x256 = 7  /* CTA pair, 256 rows per CTA: two UMMA 256x256 per K step */
+  OXGPU_VARIANT_2CTA_512x256 = 7, /* CTA pair, 256 rows per CTA: two UMMA 256x256 per K step */
+  OXGPU_VARIANT_1CTA_256x256 = 8  /* one CTA, two UMMA 128x256 sharing B */
 };
 #define OXGPU_FLAG_VARIANT(v) ((unsigned)(v) & 0xffu)
 #define OXGPU_FLAG_STAGES(s) (((unsigned)(s) & 0xfu) << 8)    /* 0 = deepest that fits */

@@ -27,6 +27,7 @@ enum Variant {
   VARIANT_2CTA_256x128 = 5,
   VARIANT_SPLITK = 6,
   VARIANT_2CTA_512x256 = 7,
+  VARIANT_1CTA_256x256 = 8,
 };
 
 // Every tcgen05 GEMM kernel here runs 10 warps: TMA producer, MMA issuer (also
@@ -65,6 +66,7 @@ inline VariantShape variant_shape(int variant) {
     case VARIANT_2CTA_256x256: return {2, 256, 256, 128, 128};
     case VARIANT_2CTA_256x128: return {2, 256, 128, 128, 64};
     case VARIANT_2CTA_512x256: return {2, 512, 256, 256, 128};
+    case VARIANT_1CTA_256x256: return {1, 256, 256, 256, 256};
     default: return {0, 0, 0, 0, 0};
   }
 }
