@@ -86,9 +86,13 @@ OXGPU_API int oxgpu_b200_kernel_binding(const oxgpu_tile_config *c, const char *
 OXGPU_API int oxgpu_b200_choose_config(int m, int n, int k, oxgpu_tile_config *out);
 
 /* `emit_gemm_ptx --info` (test/emit_gemm_ptx.ml:39-43): launch facts of a
- * catalog entry.  Reports the B200 kernel that serves `name`: CTA width,
- * dynamic shared bytes and total shared bytes.  `name` is one of the ten
- * entry symbols (examples/kernels/gemm.ml:165-199, gemm_bf16.ml:130-132). */
+ * catalog entry.  Reports the B200 kernel with the entry's own tile shape: CTA
+ * width, dynamic shared bytes and total shared bytes.  (When M and N are
+ * multiples of 256 the entry is launched on the one-CTA 256x256 kernel instead,
+ * with the same CTA width and at most 227 KiB of shared memory; the library
+ * launches the kernels itself, so these figures are informational.)  `name` is
+ * one of the ten entry symbols (examples/kernels/gemm.ml:165-199,
+ * gemm_bf16.ml:130-132). */
 OXGPU_API int oxgpu_b200_kernel_info(const char *name, int *threads, int *dynamic_smem,
                                      int *total_smem);
 
@@ -163,8 +167,9 @@ OXGPU_API int oxgpu_b200_encode_tmap_2d(void *map_out, const void *device_ptr, i
  * device f32 pointer with row stride (n/bn)*bn = n.  Requires m % bm == 0,
  * n % bn == 0, k % BK == 0 like the reference (bench/bench.py:247-250); BK is
  * 32 for the f32 entries and 64 for gemm_bf16_fast.  The library serves every
- * name with a 128-row (or 256-row) tcgen05 tile; bm=64 entries therefore also
- * need m % 128 == 0.  Replaces cuLaunchKernel(fn, n/bn, m/bm, 1, threads, ...). */
+ * name with a 128-row (or 256-row) tcgen05 tile, issuing the per-stage loads in
+ * units of the caller's boxes; bm=64 entries therefore also need m % 128 == 0.
+ * Replaces cuLaunchKernel(fn, n/bn, m/bm, 1, threads, ...). */
 OXGPU_API int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uint64_t c,
                                    int m, int n, int k, void *stream);
 

@@ -31,8 +31,7 @@ struct Staging {
   void *a = nullptr, *bt = nullptr, *c = nullptr;
   size_t a_bytes = 0, bt_bytes = 0, c_bytes = 0;
   cudaStream_t in = nullptr, compute = nullptr, out = nullptr;
-  cudaEvent_t bt_ready = nullptr;
-  cudaEvent_t a_ready[64] = {}, c_ready[64] = {};
+  cudaEvent_t a_ready[64] = {}, c_ready[64] = {};  // upload-landed / block-computed, one slot per step
   bool events = false;
 };
 
@@ -390,7 +389,6 @@ int ensure_staging(Staging &s, size_t a_bytes, size_t bt_bytes, size_t c_bytes) 
     OX_CUDA(cudaStreamCreateWithFlags(&s.out, cudaStreamNonBlocking));
   }
   if (!s.events) {
-    OX_CUDA(cudaEventCreateWithFlags(&s.bt_ready, cudaEventDisableTiming));
     for (int i = 0; i < 64; i++) {
       OX_CUDA(cudaEventCreateWithFlags(&s.a_ready[i], cudaEventDisableTiming));
       OX_CUDA(cudaEventCreateWithFlags(&s.c_ready[i], cudaEventDisableTiming));
