@@ -476,6 +476,28 @@ def test_bf16_projection_shapes(m, n, k):
         assert float((c - exact).abs().max()) <= tol and float((cs - exact).abs().max()) <= tol
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_shards_concatenate_to_the_unsharded_result(world):
+    """The multi-GPU driver's decomposition, run shard by shard on one GPU: every
+    rank's C[:, n0:n1] = A * B[:, n0:n1] and the concatenation equals the
+    unsharded GEMM bit for bit (same kernel, same K order per output)."""
+    from oxcamlgpu_b200 import sharded
+    m, n, k = 1024, 8192, 512
+    a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 4, 1.0, 0)
+    gemm.fill_normal(bt, 4, 1.0, m * k)
+    whole = gemm.gemm_bf16(a, bt)
+    parts = sharded.column_partition(n, world)
+    shards = [gemm.gemm_bf16(a, bt[n0:n1]) for n0, n1 in parts]
+    assert torch.equal(torch.cat(shards, dim=1), whole)
+    # the gathered layout [world, M, N/world] and its re-interleave
+    gathered = torch.stack(shards, dim=0)
+    assert torch.equal(sharded.blocks_to_row_major(gathered), whole)
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
+    assert float((whole - exact).abs().max()) <= strict_tol(k, float(a.float().abs().max()), float(bt.float().abs().max()))
+
+
 def test_launch_count_increases():
     before = gemm.launch_count()
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
