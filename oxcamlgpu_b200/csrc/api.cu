@@ -226,8 +226,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   const long long work = (long long)p.tiles_m * p.tiles_n * p.splits;
   if (work <= 0 || work > 0x7fffffffLL) return fail(OXGPU_E_TOO_LARGE, "too many tiles");
 
-  cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof cfg);
+  cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreadsPerCta, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
@@ -302,7 +301,7 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   if (st) return st;
   if (out16 && (ldc * 2) % 16) return fail(OXGPU_E_ALIGN, "bf16 C needs ldc to be a multiple of 8");
   int dev_index;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
 
   int variant = (int)(flags & 0xffu);
@@ -428,7 +427,7 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
   if (((int64_t)k * esize) % 16 || n % 4)
     return fail(OXGPU_E_SHAPE, "rows of A/B^T must be multiples of 16 bytes and N a multiple of 4");
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   Staging &s = dev->staging;
   std::lock_guard<std::mutex> lock(g_staging_mutex);
@@ -545,7 +544,7 @@ int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uin
   if (m % shape.tile_m)
     return fail(OXGPU_E_SHAPE, "this entry is served by a 128-row tcgen05 tile: M must be a multiple of 128");
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   GemmParams p;
   std::memset(&p, 0, sizeof p);
@@ -618,7 +617,7 @@ int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16_t *bt, fl
   if (splits < 0 || splits > 255) return fail(OXGPU_E_INVALID_ARG, "splits must be in [0, 255]");
   if (n % 4) return fail(OXGPU_E_SHAPE, "split-K needs N to be a multiple of 4");
   int dev_index;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   // the slice count the split-K path will settle on (same rule as the
   // workspace entry point), so the size can be refused before anything runs
@@ -664,7 +663,7 @@ int oxgpu_b200_gemm_exact(const void *a, const void *bt, float *c, int m, int n,
     return fail(OXGPU_E_INVALID_ARG, "leading dimension smaller than the row length");
   if (input_mode < 0 || input_mode > 2) return fail(OXGPU_E_INVALID_ARG, "input_mode must be 0, 1 or 2");
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   dim3 grid((n + kSimtTile - 1) / kSimtTile, (m + kSimtTile - 1) / kSimtTile, 1);
   if (grid.y > 65535) return fail(OXGPU_E_TOO_LARGE, "M too large for the exact kernel's grid");
@@ -686,7 +685,7 @@ int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_byte
   if (element_bytes != 2 && element_bytes != 4)
     return fail(OXGPU_E_INVALID_ARG, "element_bytes must be 2 or 4");
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   dim3 grid((n + 31) / 32, (k + 31) / 32, 1), block(32, 8, 1);
   if (grid.y > 65535) return fail(OXGPU_E_TOO_LARGE, "K too large for the transpose grid");
@@ -704,7 +703,7 @@ int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *
   if (!src || !dst) return fail(OXGPU_E_INVALID_ARG, "null pointer");
   if (count == 0) return OXGPU_OK;
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   size_t blocks = (count + 255) / 256;
   if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
@@ -726,7 +725,7 @@ int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *
 
 int oxgpu_b200_release_staging(void) {
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   std::lock_guard<std::mutex> lock(g_staging_mutex);
   Staging &s = dev->staging;
@@ -746,7 +745,7 @@ static int fill(int dist, void *dst, size_t count, int element_bytes, uint32_t s
     return fail(OXGPU_E_INVALID_ARG, "element_bytes must be 2 or 4");
   if (count == 0) return OXGPU_OK;
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   size_t blocks = (count + 255) / 256;
   if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
@@ -773,7 +772,7 @@ int oxgpu_b200_fill_normal(void *dst, size_t count, int element_bytes, uint32_t 
 
 int oxgpu_b200_device_status(uint32_t words[8]) {
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   OX_CUDA(cudaDeviceSynchronize());
   uint32_t host[8];
@@ -793,7 +792,7 @@ int oxgpu_b200_device_status(uint32_t words[8]) {
 
 int oxgpu_b200_selftest_bounded_wait(uint64_t budget_ns) {
   int dev_index, st;
-  DeviceState *dev;
+  DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   if (budget_ns == 0 || budget_ns > 1000000000ull)
     return fail(OXGPU_E_INVALID_ARG, "self-test budget must be in (0, 1 s]");
