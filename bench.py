@@ -373,8 +373,10 @@ def main():
             host_fn(a_h, bt_h, c_h, flags)           # returns when C is on the host
         sec = time.perf_counter() - t0
         sec = reduce_max(sec)
-        if not torch.equal(c_h[rows.cpu()], c[rows].cpu()):
-            raise SystemExit("host-buffer path disagrees with the device-resident path")
+        # (block-wise GEMMs may pick other tiles or K slicings than the whole problem:
+        # same tolerance as against the exact kernel, not bit equality)
+        if not float((c_h[rows.cpu()] - exact.cpu()).abs().max()) <= tol:
+            raise SystemExit("host-buffer path disagrees with the exact kernel")
         e2e = {"value": flops_all / (sec / e2e_steps) * 1e-12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": (a_h.numel() + bt_h.numel()) * a_h.element_size(),
                "d2h_bytes_per_step": c_h.numel() * 4, "ms_per_step": sec / e2e_steps * 1e3,

@@ -23,7 +23,7 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kKinds = 3;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C
-constexpr int kVariants = 9;  // index by Variant value (1..5, 7 and 8 used)
+constexpr int kVariants = 11;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
 
@@ -177,6 +177,7 @@ struct LaunchPlan {
   int splits, kb_per_split, split_row_stride;
   int reorder_kb = -1;  // -1: library default
   bool out16 = false;   // bf16 C
+  int cluster_splits = 0;  // > 1: split-K across a cluster of that many CTAs (one-CTA 128-row tiles)
 };
 
 // K blocks issued block-major at either end of a tile (two-row-block tiles).
@@ -193,6 +194,11 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   const int most = variant_max_stages(plan.variant);
   if (stages <= 0 || stages > most) stages = most;
   if (stages < 2) stages = 2;
+  if (plan.cluster_splits > 1) {
+    // the partial tile (128 rows x tile_n f32) is parked in the operand ring
+    const int need = 128 * shape.tile_n * 4, per = variant_stage_bytes(plan.variant);
+    if (stages * per < need) stages = (need + per - 1) / per;
+  }
   const int smem = variant_smem_bytes(plan.variant, stages);
 
   const int kbe = plan.kind == 0 ? 64 : 32;
@@ -248,6 +254,16 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     }
     long long clusters = work < maxc ? work : maxc;
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  } else if (plan.cluster_splits > 1) {
+    // one work item per CTA: cluster c = tile c, CTA rank = K slice
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)plan.cluster_splits;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3((unsigned)work, 1, 1);
+    p.cluster_reduce = 1;
   } else {
     long long ctas = work < dev.sm_count ? work : dev.sm_count;
     cfg.gridDim = dim3((unsigned)ctas, 1, 1);
@@ -289,6 +305,15 @@ int choose_variant(const DeviceState &dev, int m, int n, int k) {
   if (tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
   if (tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
   if (tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
+  // Fewer tiles than SMs: these problems stream one operand from HBM and the
+  // time is set by the busiest SM's bytes.  A full wave of one-CTA tiles first
+  // (128-column tiles stream B^T faster than 256-column ones when M is a single
+  // tile row: 111 us against 173 us at 128 x 28672 x 8192) ...
+  if (tiles(128, 256) >= dev.sm_count) return VARIANT_1CTA_128x256;
+  if (tiles(128, 128) >= dev.sm_count) return VARIANT_1CTA_128x128;
+  // ... otherwise, when K is long, split it across a cluster so every SM has work.
+  if (k >= 2048 && tiles(128, 256) * 2 <= dev.sm_count && n % 256 == 0) return VARIANT_CLUSTER_SPLITK_128x256;
+  if (k >= 2048 && tiles(128, 128) * 2 <= dev.sm_count) return VARIANT_CLUSTER_SPLITK_128x128;
   if (tiles(128, 256) >= dev.sm_count / 2) return VARIANT_1CTA_128x256;
   return VARIANT_1CTA_128x128;
 }
@@ -310,8 +335,29 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   int splits = (int)((flags >> 20) & 0xffu);
   const bool splitk = variant == VARIANT_SPLITK;
   const bool was_auto = variant == VARIANT_AUTO;
-  if (was_auto) variant = choose_variant(*dev, m, n, k);
+  if (was_auto) {
+    variant = choose_variant(*dev, m, n, k);
+    if (out16 && (variant == VARIANT_CLUSTER_SPLITK_128x256 || variant == VARIANT_CLUSTER_SPLITK_128x128))
+      variant = VARIANT_1CTA_128x128;  // the cluster reduction writes f32 only
+  }
   if (splitk) variant = VARIANT_1CTA_128x128;
+  int cluster_splits = 0;
+  if (variant == VARIANT_CLUSTER_SPLITK_128x256 || variant == VARIANT_CLUSTER_SPLITK_128x128) {
+    if (out16) return fail(OXGPU_E_INVALID_ARG, "cluster split-K writes f32 C only");
+    const int tile_n = variant == VARIANT_CLUSTER_SPLITK_128x256 ? 256 : 128;
+    variant = tile_n == 256 ? VARIANT_1CTA_128x256 : VARIANT_1CTA_128x128;
+    const int num_kb = (k + (kind == 0 ? 64 : 32) - 1) / (kind == 0 ? 64 : 32);
+    const long long tiles = (long long)((m + 127) / 128) * ((n + tile_n - 1) / tile_n);
+    int s = splits;
+    if (s <= 0) {  // as many slices as fill the GPU once, a power of two, at most 8
+      s = 8;
+      while (s > 1 && tiles * s > dev->sm_count) s >>= 1;
+    }
+    while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) s >>= 1;  // every slice gets a K block
+    if (s != 1 && s != 2 && s != 4 && s != 8)
+      return fail(OXGPU_E_INVALID_ARG, "cluster split-K takes 2, 4 or 8 slices");
+    cluster_splits = s;  // 1: nothing to split, plain kernel
+  }
   if (out16 && !splitk && !kernel_for(0, variant, true)) {
     if (!was_auto) return fail(OXGPU_E_INVALID_ARG, "this variant has no bf16-output kernel");
     variant = VARIANT_1CTA_128x128;
@@ -322,6 +368,12 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   const int kbe = kind == 0 ? 64 : 32;
 
   LaunchPlan plan{kind, variant, stages, group_m, 1, 0, 0};
+  if (cluster_splits > 1) {
+    const int num_kb = (k + kbe - 1) / kbe;
+    plan.cluster_splits = cluster_splits;
+    plan.splits = cluster_splits;
+    plan.kb_per_split = (num_kb + cluster_splits - 1) / cluster_splits;
+  }
   const int reorder_field = (int)((flags >> 28) & 0xfu);  // 0 default, 15 off, else that many K blocks
   plan.reorder_kb = reorder_field == 0 ? -1 : (reorder_field == 15 ? 0 : reorder_field);
   GemmParams p;
@@ -344,6 +396,10 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   if (!splitk) {
     if ((st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32)))
       return st;
+    p.c_ptr = c;
+    p.c_ld = ldc;
+    p.c_rows = m;
+    p.c_cols = n;
     return launch_umma(*dev, plan, p, m, n, k, stream);
   }
 

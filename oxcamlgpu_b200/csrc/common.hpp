@@ -28,6 +28,8 @@ enum Variant {
   VARIANT_SPLITK = 6,
   VARIANT_2CTA_512x256 = 7,
   VARIANT_1CTA_256x256 = 8,
+  VARIANT_CLUSTER_SPLITK_128x256 = 9,   // K slices across a cluster, reduced through DSMEM
+  VARIANT_CLUSTER_SPLITK_128x128 = 10,
 };
 
 // Every tcgen05 GEMM kernel here runs 10 warps: TMA producer, MMA issuer (also

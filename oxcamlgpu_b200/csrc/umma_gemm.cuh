@@ -73,6 +73,15 @@ struct GemmParams {
   // L2 eviction priority of the A loads, the B^T loads and the C stores:
   // 0 = normal, 1 = evict first, 2 = evict last.
   int hint_a, hint_b, hint_c;
+  // Split-K inside a thread-block cluster (one-CTA 128-row tiles only): the
+  // `splits` CTAs of a cluster take the K slices of one tile, leave their
+  // partial tiles in their own shared memory, and each CTA then sums one column
+  // range of the tile across the cluster through distributed shared memory and
+  // writes it to C.  No workspace, no second kernel, fixed summation order.
+  int cluster_reduce;
+  float *c_ptr;
+  long long c_ld;
+  int c_rows, c_cols;
   unsigned long long wait_budget_ns;
 };
 
@@ -461,6 +470,26 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
       ptx::tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                               (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
+      if constexpr (CTA_GROUP == 1 && MI == 1) {
+        if (p.cluster_reduce) {
+          // Leave this CTA's partial tile in its own shared memory, in the (now
+          // idle) operand ring: row r at r * BN * 4 bytes, 16-byte pieces
+          // XOR-swizzled by r % 8 inside each 128-byte group.
+          const uint32_t row_base = smem_base + (uint32_t)(quad * 32 + lane) * (uint32_t)(BN * 4);
+#pragma unroll 1
+          for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c * 32), v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const uint32_t piece = (uint32_t)((ch_begin + c) * 8 + j) ^ (uint32_t)(lane & 7);
+              ptx::st_shared_v4(row_base + (piece << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          }
+          continue;  // exactly one work item per CTA in this mode
+        }
+      }
       auto release_unit = [&]() {
         // the unit is in registers everywhere in this warp: hand it back to
         // the issuer before finishing the stores
@@ -531,6 +560,56 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     if (lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
+  }
+
+  // ---- split-K reduction across the cluster --------------------------------------
+  if constexpr (CTA_GROUP == 1 && MI == 1) {
+    if (p.cluster_reduce) {
+      // Every thread of every CTA passes both cluster barriers, whatever
+      // happened in its role (a timed-out wait included), so nobody is left
+      // waiting; the data is only meaningful if no wait timed out, which the
+      // status block tells the host.
+      __syncthreads();
+      ptx::cluster_arrive();
+      ptx::cluster_wait();  // all partial tiles of the cluster are in place
+      if (warp >= 2 && blockIdx.x < (unsigned)total_work) {
+        const int S = p.splits;
+        const int rank = (int)(blockIdx.x % (unsigned)S);
+        const int t = (int)(blockIdx.x / (unsigned)S);
+        int tm, tn;
+        grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+        const int pieces_per_row = (BN / 4) / S;  // this CTA's column range, in 16-byte pieces
+        const int row0 = tm * 128, col0 = tn * BN;
+        uint32_t peer_base[8];
+        for (int s2 = 0; s2 < S && s2 < 8; s2++) peer_base[s2] = ptx::map_to_cta(smem_base, (uint32_t)s2);
+        for (int i = (int)threadIdx.x - 64; i < 128 * pieces_per_row; i += kThreadsPerCta - 64) {
+          const int r = i / pieces_per_row, pj = i - r * pieces_per_row;
+          const int pc = rank * pieces_per_row + pj;
+          const uint32_t off = (uint32_t)r * (uint32_t)(BN * 4) + (((uint32_t)pc ^ (uint32_t)(r & 7)) << 4);
+          float4 acc = ptx::ld_shared_cluster_v4(peer_base[0] + off);
+          for (int s2 = 1; s2 < S; s2++) {  // slices in ascending order: deterministic
+            const float4 v = ptx::ld_shared_cluster_v4(peer_base[s2] + off);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+          }
+          const int row = row0 + r, col = col0 + pc * 4;
+          if (row < p.c_rows) {
+            float *dst = p.c_ptr + (long long)row * p.c_ld + col;
+            if (col + 4 <= p.c_cols) {
+              *reinterpret_cast<float4 *>(dst) = acc;
+            } else {
+              const float e[4] = {acc.x, acc.y, acc.z, acc.w};
+              for (int q = 0; q < 4; q++)
+                if (col + q < p.c_cols) dst[q] = e[q];
+            }
+          }
+        }
+      }
+      ptx::cluster_arrive();
+      ptx::cluster_wait();  // nobody retires while a peer may still read its shared memory
+    }
   }
 
   // ---- teardown -----------------------------------------------------------------

@@ -345,6 +345,40 @@ def test_split_k(m, n, k, splits):
     check_bf16(a_bits, bt_bits, c)
 
 
+@pytest.mark.parametrize("variant,splits", [("cluster_splitk_128x128", 2), ("cluster_splitk_128x128", 4),
+                                            ("cluster_splitk_128x256", 2), ("cluster_splitk_128x256", 4),
+                                            ("cluster_splitk_128x256", 8), ("cluster_splitk_128x128", 0)])
+@pytest.mark.parametrize("m,n,k", [(128, 1024, 2048), (100, 520, 1000), (384, 512, 4096), (128, 256, 64)])
+def test_cluster_split_k(variant, splits, m, n, k):
+    """K slices across a thread-block cluster, summed through distributed shared
+    memory: same slices and summation order as the workspace split-K, so the
+    two agree bit for bit; ragged edges and NaN guard bands as elsewhere."""
+    rng = np.random.default_rng(splits * 13 + k)
+    a_bits, bt_bits = rand_bf16(rng, m, k, 0.02), rand_bf16(rng, n, k, 0.02)
+    pad = torch.full((m + 2, n + 8), float("nan"), device=DEV)
+    c = pad[1:m + 1, 4:n + 4]
+    gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), c, flags=gemm.make_flags(variant, splits=splits))
+    check_bf16(a_bits, bt_bits, c.contiguous())
+    assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
+    assert torch.isnan(pad[:, :4]).all() and torch.isnan(pad[:, n + 4:]).all()
+    if splits in (2, 4) and (k // 64) % splits == 0:
+        ws = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), flags=gemm.make_flags("splitk", splits=splits))
+        assert torch.equal(c.contiguous(), ws)
+
+
+def test_skinny_problem_takes_the_cluster_split_k_path_by_default():
+    a = torch.empty(128, 8192, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(8192, 8192, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 3, 0.02, 0)
+    gemm.fill_normal(bt, 3, 0.02, 128 * 8192)
+    auto = gemm.gemm_bf16(a, bt)
+    explicit = gemm.gemm_bf16(a, bt, flags=gemm.make_flags("cluster_splitk_128x256", splits=4))
+    assert torch.equal(auto, explicit)
+    tf = gemm.gemm_tf32(a.float(), bt.float())
+    exact = gemm.gemm_exact(a.float(), bt.float(), gemm.INPUT_TF32)
+    assert float((tf - exact).abs().max()) <= tc_tol(8192, float(a.float().abs().max()), float(bt.float().abs().max()))
+
+
 # ---- helpers ---------------------------------------------------------------------------
 def test_conversion_and_transpose_match_the_oracle(golden_dir):
     g = np.load(os.path.join(golden_dir, "rounding_edges.npz"))
