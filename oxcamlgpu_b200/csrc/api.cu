@@ -218,8 +218,10 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   // C is written once and never read by this kernel: its stores are marked
   // evict-first so the output stream does not push operand tiles out of L2
   // (worth 6 points on 32768^2-sized outputs, nothing at 8192^3).
-  p.hint_a = 0;
-  p.hint_b = 0;
+  // (Operands are kept with evict-last priority when both fit a few times over
+  // in L2-sized waves: +1 point up to 576 MiB of A + B^T, -3 points at 1 GiB.)
+  const double operand_bytes = ((double)m * k + (double)n * k) * (plan.kind == 0 ? 2 : 4);
+  p.hint_a = p.hint_b = operand_bytes <= 768.0 * 1024 * 1024 ? 2 : 0;
   p.hint_c = 1;
   p.wait_budget_ns = wait_budget_ns();
 
