@@ -44,8 +44,8 @@ WORKLOADS = {
     "cfg5": ("bf16", 32768, 65536, 8192, "normal", 1.0, 4),
 }
 # DRAM bytes (read + write) of one launch of the dominant kernel, from one ncu
-# capture of the same kernel (profiles/umma_gemm_bf16_8192.md); None = not captured.
-NCU_TRAFFIC_BYTES = {"bf16_8192": 1.085e9}
+# capture of the same kernel (profiles/umma_gemm_*.md); None = not captured.
+NCU_TRAFFIC_BYTES = {"bf16_8192": 1.085e9, "tf32_4096": 0.247e9, "proj_c": 0.1405e9}
 
 
 def measured_peaks():
@@ -392,14 +392,22 @@ def main():
     per_launch_flops = 2.0 * m * n * k
     kernel_ms = sum(ours_ms) / len(ours_ms)            # this rank's average launch duration
     achieved = per_launch_flops / (kernel_ms * 1e-3) * 1e-12
-    roofline = {
-        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+    algorithmic_bytes = (m * k + n * k) * a.element_size() + m * n * 4
+    ridge = peak * 1e12 / (peaks["hbm_gbs"] * 1e9)              # flop per byte where the two roofs meet
+    if per_launch_flops / algorithmic_bytes >= ridge:
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak,
+                    "peak_source": ("burst cuBLAS bf16 8192^3 of %s" % peaks["source"]) +
+                                   ("" if kind == "bf16" else " / 2 (no TF32 figure measured)")}
+    else:                                                       # skinny shapes stream one operand
+        gbs = algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "peak_source": "copy bandwidth of %s" % peaks["source"]}
+    roofline.update({
         "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-        "peak_source": ("burst cuBLAS bf16 8192^3 of %s" % peaks["source"]) +
-                       ("" if kind == "bf16" else " / 2 (no TF32 figure measured)"),
-        "algorithmic_bytes": (m * k + n * k) * a.element_size() + m * n * 4,
-        "hbm_frac_of_measured": ((m * k + n * k) * a.element_size() + m * n * 4) / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-    }
+        "algorithmic_bytes": algorithmic_bytes,
+        "hbm_frac_of_measured": algorithmic_bytes / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+    })
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
