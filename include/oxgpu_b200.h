@@ -251,7 +251,7 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
  * and launches nothing (e.g. m=128, n=8192 allows up to 8 slices).  n % 4 == 0.
  *
  * The first call on each device looks up the array's device address (with that
- * device current); make that first call before starting any stream capture.
+ * device current) and later calls reuse it.
  * Neither that set-up nor any later call uses cudaMalloc, cudaFree or an
  * allocating library routine.  All calls on a device share the one array and it
  * keeps whatever the previous call left in it; that is harmless here, because
