@@ -209,7 +209,7 @@ def main():
     ap.add_argument("--variant", default="auto")
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
-    ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of C (N > 1)")
+    ap.add_argument("--gather", action="store_true", help="also time a replicated C: NCCL all-gather vs the fused fan-out epilogue (N > 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-flush", action="store_true", help="back-to-back launches, no L2 flush")
@@ -349,11 +349,38 @@ def main():
     del c_ref
 
     gather_ms = None
+    gather = None
     if args.gather and world > 1:
-        drv = sharded.ColumnShardedGemm(m, global_n, k, flags=flags) if args.workload == "cfg5" else None
-        g_ms = timed_steps(lambda: sharded.all_gather_c(c), max(3, args.steps // 5), 2)
+        # A replicated row-major C, two ways.  Separate: GEMM, NCCL all-gather of the
+        # shards, re-interleave of the gathered blocks.  Fused: the GEMM's fan-out
+        # epilogue stores every tile into all ranks' C over NVLink as it is produced.
+        g_steps = max(3, args.steps // 5)
+        g_ms = timed_steps(lambda: sharded.all_gather_c(c), g_steps, 2)
         gather_ms = reduce_max(statistics.median(g_ms))
-        del drv
+        sep_ms = timed_steps(lambda: (run_gemm(), sharded.blocks_to_row_major(sharded.all_gather_c(c))), g_steps, 2)
+        sep_med = reduce_max(statistics.median(sep_ms))
+        torch.cuda.empty_cache()
+        fused = sharded.FusedGatherGemm(m, global_n, k, flags=flags)
+        if (fused.n0, fused.n1) != (n0, n0 + n):
+            raise SystemExit("fused gather: shard windows disagree with the bench's partition")
+        fused_ms = timed_steps(lambda: fused.run(a, bt), g_steps, 2)
+        fused_med = reduce_max(statistics.median(fused_ms))
+        full = fused.finish()
+        # every rank's window of this rank's replica against that rank's own C rows
+        mine = c[rows].contiguous()
+        theirs = torch.empty(world * rows.numel(), n, device=dev)
+        dist.all_gather_into_tensor(theirs, mine)
+        theirs = theirs.view(world, rows.numel(), n).permute(1, 0, 2).reshape(rows.numel(), world * n)
+        if not float((full[rows] - theirs).abs().max()) <= tol:
+            raise SystemExit("fused gather: replicated C disagrees with the ranks' own shards")
+        recv_bytes = (world - 1) * m * n * 4
+        gather = {"nccl_allgather_median_ms": gather_ms, "separate_gemm_allgather_interleave_median_ms": sep_med,
+                  "fused_gemm_gather_median_ms": fused_med, "separate_over_fused": sep_med / fused_med,
+                  "nvlink_in_bytes_per_gpu": recv_bytes,
+                  "nvlink_bound_ms_at_770GBs": recv_bytes / 770e9 * 1e3,
+                  "gemm_alone_median_ms": median_ms}
+        del full, theirs
+        fused.close()
 
     # end to end through the host-buffer entry point: pinned host operands in,
     # pinned host C out, every step
@@ -444,6 +471,7 @@ def main():
         }
         if gather_ms is not None:
             line["allgather_c_median_ms"] = gather_ms
+            line["gather"] = gather
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

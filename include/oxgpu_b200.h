@@ -232,6 +232,42 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
                                       unsigned flags, void *workspace, size_t workspace_bytes,
                                       void *stream);
 
+/* GEMM with a fan-out epilogue: every tile of C is written to n_dests (1..8)
+ * destinations as it leaves the tensor cores.  (No counterpart in the reference,
+ * which has no multi-GPU path; this is the "GEMM, then all-gather of the column
+ * shards of C" of a column-sharded GEMM done by one kernel.)  c_dests[i] points
+ * at the first element of this call's [M,N] window inside destination i, a
+ * row-major f32 matrix with leading dimension ldc -- typically
+ * C_full_i + column_offset_of_this_rank, with C_full_i the replicated result in
+ * GPU i's memory.  A destination may be memory of another GPU that the caller
+ * has made addressable (peer access inside one process, or
+ * oxgpu_b200_shared_open across processes); tiles then cross NVLink as plain
+ * (non-multicast) TMA tile stores while the main loop keeps running, and arrive
+ * already interleaved in row-major order.  Same arithmetic, operand contracts and
+ * flags as oxgpu_b200_gemm_bf16 / _tf32; variants: auto, 1CTA_128x128,
+ * 2CTA_256x256, 2CTA_512x256.  A destination's contents are complete once the
+ * work on `stream` has completed on the WRITING GPU; readers on other GPUs
+ * need their own ordering after that point (a host barrier, an event). */
+OXGPU_API int oxgpu_b200_gemm_bf16_fanout(const uint16_t *a, const uint16_t *bt,
+                                          float *const *c_dests, int n_dests, int m, int n, int k,
+                                          int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
+                                          void *stream);
+OXGPU_API int oxgpu_b200_gemm_tf32_fanout(const float *a, const float *bt, float *const *c_dests,
+                                          int n_dests, int m, int n, int k, int64_t lda,
+                                          int64_t ldb, int64_t ldc, unsigned flags, void *stream);
+
+/* Device memory other processes on the same machine can map (set-up time, not
+ * the hot path): _shared_alloc allocates `bytes` on the current device and
+ * fills a 64-byte handle to send to the other processes by any host channel;
+ * _shared_open maps a handle received from another process (peer access over
+ * NVLink is enabled on first use) and returns a pointer valid in this process;
+ * _shared_close unmaps it; _shared_free releases an allocation (after every
+ * other process has closed it). */
+OXGPU_API int oxgpu_b200_shared_alloc(size_t bytes, void **ptr, unsigned char handle[64]);
+OXGPU_API int oxgpu_b200_shared_open(const unsigned char handle[64], void **ptr);
+OXGPU_API int oxgpu_b200_shared_close(void *ptr);
+OXGPU_API int oxgpu_b200_shared_free(void *ptr);
+
 /* Split-K bf16 GEMM that allocates nothing.  (No counterpart in the reference:
  * its kernels use no scratch memory at all.)
  *

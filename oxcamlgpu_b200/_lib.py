@@ -75,6 +75,14 @@ def lib() -> ctypes.CDLL:
         "oxgpu_b200_splitk_workspace_bytes": ([c_int, c_int, c_int], sz),
         "oxgpu_b200_gemm_bf16_ws": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                      ctypes.c_uint, c_void_p, sz, c_void_p], c_int),
+        "oxgpu_b200_gemm_bf16_fanout": ([c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int,
+                                         c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_gemm_tf32_fanout": ([c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int,
+                                         c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_shared_alloc": ([sz, ctypes.POINTER(c_void_p), ctypes.c_char_p], c_int),
+        "oxgpu_b200_shared_open": ([ctypes.c_char_p, ctypes.POINTER(c_void_p)], c_int),
+        "oxgpu_b200_shared_close": ([c_void_p], c_int),
+        "oxgpu_b200_shared_free": ([c_void_p], c_int),
         "oxgpu_b200_gemm_bf16_splitk_static": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64,
                                                 i64, i64, c_int, c_void_p], c_int),
         "oxgpu_b200_gemm_exact": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,

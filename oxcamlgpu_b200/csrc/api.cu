@@ -22,7 +22,7 @@ namespace oxgpu {
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kKinds = 3;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C
+constexpr int kKinds = 5;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out
 constexpr int kVariants = 11;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
@@ -162,6 +162,26 @@ const void *kernel_for(int kind, int variant, bool out16 = false) {
   return nullptr;
 }
 
+// Fan-out kernels (several destinations per C tile).
+const void *fanout_kernel_for(int kind, int variant) {
+#define OX_F(K, BM, BN, CG) ((const void *)umma_gemm_kernel<K, BM, BN, CG, false, true>)
+  if (kind == 0) {
+    switch (variant) {
+      case VARIANT_1CTA_128x128: return OX_F(0, 128, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_F(0, 128, 256, 2);
+      case VARIANT_2CTA_512x256: return OX_F(0, 256, 256, 2);
+    }
+  } else {
+    switch (variant) {
+      case VARIANT_1CTA_128x128: return OX_F(1, 128, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_F(1, 128, 256, 2);
+      case VARIANT_2CTA_512x256: return OX_F(1, 256, 256, 2);
+    }
+  }
+#undef OX_F
+  return nullptr;
+}
+
 unsigned long long wait_budget_ns() {
   static unsigned long long v = [] {
     const char *e = std::getenv("OXGPU_WAIT_BUDGET_MS");
@@ -178,6 +198,7 @@ struct LaunchPlan {
   int reorder_kb = -1;  // -1: library default
   bool out16 = false;   // bf16 C
   int cluster_splits = 0;  // > 1: split-K across a cluster of that many CTAs (one-CTA 128-row tiles)
+  bool fanout = false;     // `p` is a GemmParamsFanout and the fan-out kernel is launched
 };
 
 // K blocks issued block-major at either end of a tile (two-row-block tiles).
@@ -188,8 +209,10 @@ constexpr int kDefaultReorderKb = 3;
 int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, int n, int k,
                 cudaStream_t stream) {
   const VariantShape shape = variant_shape(plan.variant);
-  const void *fn = kernel_for(plan.kind, plan.variant, plan.out16);
+  const void *fn = plan.fanout ? fanout_kernel_for(plan.kind, plan.variant)
+                               : kernel_for(plan.kind, plan.variant, plan.out16);
   if (!fn || shape.cta_group == 0) return fail(OXGPU_E_INVALID_ARG, "unknown kernel variant");
+  const int attr_kind = plan.fanout ? 3 + plan.kind : (plan.out16 ? 2 : plan.kind);
   int stages = plan.stages;
   const int most = variant_max_stages(plan.variant);
   if (stages <= 0 || stages > most) stages = most;
@@ -225,7 +248,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   p.hint_c = 1;
   p.wait_budget_ns = wait_budget_ns();
 
-  bool &attr = dev.attr_set[plan.out16 ? 2 : plan.kind][plan.variant];
+  bool &attr = dev.attr_set[attr_kind][plan.variant];
   if (!attr) {
     OX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
     attr = true;
@@ -246,7 +269,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    int &maxc = dev.max_clusters[plan.out16 ? 2 : plan.kind][plan.variant];
+    int &maxc = dev.max_clusters[attr_kind][plan.variant];
     if (maxc == 0) {
       cfg.gridDim = dim3(2 * (dev.sm_count / 2), 1, 1);
       int nc = 0;
@@ -437,6 +460,51 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   OX_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return OXGPU_OK;
+}
+
+// GEMM whose C tiles go to several destinations (see GemmParamsFanout).
+int gemm_fanout(int kind, const void *a, const void *bt, float *const *dests, int n_dests, int m, int n,
+                int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags, cudaStream_t stream) {
+  const int esize = kind == 0 ? 2 : 4;
+  if (!dests || n_dests < 1 || n_dests > kMaxFanout)
+    return fail(OXGPU_E_INVALID_ARG, "the number of destinations must be between 1 and 8");
+  int st;
+  for (int d = 0; d < n_dests; d++)
+    if ((st = check_buffers(a, bt, dests[d], m, n, k, lda, ldb, ldc, esize))) return st;
+  int dev_index;
+  DeviceState *dev = nullptr;
+  if ((st = current_device(&dev_index, &dev))) return st;
+
+  int variant = (int)(flags & 0xffu);
+  if (variant == VARIANT_AUTO) {
+    auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
+    const int pairs = dev->sm_count / 2;
+    variant = tiles(512, 256) >= pairs   ? VARIANT_2CTA_512x256
+              : tiles(256, 256) >= pairs ? VARIANT_2CTA_256x256
+                                         : VARIANT_1CTA_128x128;
+  }
+  if (!fanout_kernel_for(kind, variant))
+    return fail(OXGPU_E_INVALID_ARG, "this variant has no fan-out kernel (use 1cta_128x128, 2cta_256x256 or 2cta_512x256)");
+  const VariantShape shape = variant_shape(variant);
+  const int kbe = kind == 0 ? 64 : 32;
+
+  LaunchPlan plan{kind, variant, (int)((flags >> 8) & 0xfu), (int)((flags >> 12) & 0xffu), 1, 0, 0};
+  const int reorder_field = (int)((flags >> 28) & 0xfu);
+  plan.reorder_kb = reorder_field == 0 ? -1 : (reorder_field == 15 ? 0 : reorder_field);
+  plan.fanout = true;
+  GemmParamsFanout p;
+  std::memset((void *)&p, 0, sizeof p);
+  p.a_box_rows = shape.cta_a_rows;
+  p.b_box_rows = shape.cta_b_rows;
+  if ((st = encode_2d(&p.map_a, a, esize, (uint64_t)k, (uint64_t)m, (uint64_t)lda * esize, kbe, p.a_box_rows)))
+    return st;
+  if ((st = encode_2d(&p.map_b, bt, esize, (uint64_t)k, (uint64_t)n, (uint64_t)ldb * esize, kbe, p.b_box_rows)))
+    return st;
+  for (int d = 0; d < n_dests; d++)
+    if ((st = encode_2d(&p.dest_maps[d], dests[d], 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32)))
+      return st;
+  p.n_dests = n_dests;
+  return launch_umma(*dev, plan, p, m, n, k, stream);
 }
 
 int ensure_staging(Staging &s, size_t a_bytes, size_t bt_bytes, size_t c_bytes) {
@@ -656,6 +724,58 @@ int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, float *c, int
                             size_t workspace_bytes, void *stream) {
   return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, workspace, workspace_bytes,
                       (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_bf16_fanout(const uint16_t *a, const uint16_t *bt, float *const *c_dests, int n_dests,
+                                int m, int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                unsigned flags, void *stream) {
+  return oxgpu::gemm_fanout(0, a, bt, c_dests, n_dests, m, n, k, lda, ldb, ldc, flags, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_tf32_fanout(const float *a, const float *bt, float *const *c_dests, int n_dests, int m,
+                                int n, int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
+                                void *stream) {
+  return oxgpu::gemm_fanout(1, a, bt, c_dests, n_dests, m, n, k, lda, ldb, ldc, flags, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_shared_alloc(size_t bytes, void **ptr, unsigned char handle[64]) {
+  using namespace oxgpu;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes in the C ABI");
+  if (!ptr || !handle || bytes == 0) return fail(OXGPU_E_INVALID_ARG, "null argument or zero size");
+  void *q = nullptr;
+  OX_CUDA(cudaMalloc(&q, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, q);
+  if (e != cudaSuccess) {
+    cudaFree(q);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  std::memcpy(handle, &h, 64);
+  *ptr = q;
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_shared_open(const unsigned char handle[64], void **ptr) {
+  using namespace oxgpu;
+  if (!ptr || !handle) return fail(OXGPU_E_INVALID_ARG, "null argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  OX_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_shared_close(void *ptr) {
+  using namespace oxgpu;
+  if (!ptr) return OXGPU_OK;
+  OX_CUDA(cudaIpcCloseMemHandle(ptr));
+  return OXGPU_OK;
+}
+
+int oxgpu_b200_shared_free(void *ptr) {
+  using namespace oxgpu;
+  if (!ptr) return OXGPU_OK;
+  OX_CUDA(cudaFree(ptr));
+  return OXGPU_OK;
 }
 
 // ---- split-K without any allocation ------------------------------------------------

@@ -34,6 +34,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "common.hpp"
 #include "ptx.cuh"
 
@@ -83,6 +85,20 @@ struct GemmParams {
   long long c_ld;
   int c_rows, c_cols;
   unsigned long long wait_budget_ns;
+};
+
+// Parameters of the fan-out kernels: the epilogue writes every staged 32x32
+// sub-tile of C to `n_dests` destinations instead of one.  A destination is a
+// row-major f32 matrix with this GEMM's rows and a column window of its own;
+// it may live in this GPU's memory or in a peer's (mapped into this process),
+// which turns "GEMM, then all-gather of the column shards" into one kernel: a
+// rank's tiles leave over NVLink as they are produced, already interleaved
+// into the replicated row-major C.  The stores are ordinary (non-multicast)
+// TMA tile stores; map_c of the base struct is unused.
+constexpr int kMaxFanout = 8;
+struct GemmParamsFanout : GemmParams {
+  CUtensorMap dest_maps[kMaxFanout];
+  int n_dests;
 };
 
 struct WaitCtx {
@@ -143,9 +159,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
 // OUT16: C is stored as bf16 (round to nearest even) instead of f32 -- the
 // narrow-output epilogue the reference lists as future work
 // (docs/roadmap.md:67-71); the C map is then a bf16 map with 64-column boxes.
-template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false>
+template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
-umma_gemm_kernel(const __grid_constant__ GemmParams p) {
+umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmParamsFanout, GemmParams>::type p) {
+  static_assert(!(FANOUT && OUT16), "the fan-out epilogue writes f32");
   // A CTA owns BM_CTA rows of the tile as MI blocks of 128 rows (one UMMA each
   // per K step, all sharing the staged B^T rows).  Block `mi` of accumulator
   // set `set` is one hand-off unit between the issuer and the epilogue.
@@ -220,7 +237,11 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(map_a);
     ptx::prefetch_tensormap(map_b);
-    ptx::prefetch_tensormap(map_c);
+    if constexpr (FANOUT) {
+      for (int d = 0; d < p.n_dests; d++) ptx::prefetch_tensormap(&p.dest_maps[d]);
+    } else {
+      ptx::prefetch_tensormap(map_c);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc<CTA_GROUP>(tmem_slot, TMEM_COLS);
@@ -525,7 +546,14 @@ umma_gemm_kernel(const __grid_constant__ GemmParams p) {
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
+            if constexpr (FANOUT) {
+              // one bulk group per sub-tile: the staging buffer is reused once
+              // every destination's store has read it
+              for (int d = 0; d < p.n_dests; d++)
+                ptx::tma_store_2d_hint(&p.dest_maps[d], c_col0 + c * 32, c_row, buf, pol_c);
+            } else {
+              ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
+            }
             ptx::tma_store_commit();
           }
         }

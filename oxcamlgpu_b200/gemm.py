@@ -135,6 +135,79 @@ def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, 
     return c
 
 
+def gemm_fanout(a: torch.Tensor, bt: torch.Tensor, dests, ldc: int | None = None, flags: int = 0,
+                stream=None) -> None:
+    """C = A * B written to every destination in `dests` by one kernel (bf16 or
+    f32/TF32 operands by dtype).  A destination is either an f32 tensor view
+    [M,N] with unit column stride (its row stride must equal `ldc` of the
+    others) or a raw device address (int) of the window's first element, in
+    which case `ldc` is required -- the form used for windows inside another
+    process's memory."""
+    kind = {torch.bfloat16: "bf16", torch.float32: "tf32"}.get(a.dtype)
+    if kind is None:
+        raise ValueError("operands must be bf16 or f32")
+    m, n, k = _check_operands(a, bt, a.dtype)
+    ptrs = []
+    for d in dests:
+        if isinstance(d, int):
+            ptrs.append(d)
+            continue
+        if d.dtype != torch.float32 or d.stride(1) != 1 or tuple(d.shape) != (m, n):
+            raise ValueError("a destination must be f32 [M,N] with unit column stride")
+        if ldc is None:
+            ldc = d.stride(0)
+        if d.stride(0) != ldc:
+            raise ValueError("all destinations share one leading dimension")
+        ptrs.append(d.data_ptr())
+    if ldc is None:
+        raise ValueError("ldc is required when destinations are raw addresses")
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    fn = lib().oxgpu_b200_gemm_bf16_fanout if kind == "bf16" else lib().oxgpu_b200_gemm_tf32_fanout
+    check(fn(a.data_ptr(), bt.data_ptr(), arr, len(ptrs), m, n, k, a.stride(0), bt.stride(0), ldc, flags,
+             ctypes.c_void_p(_stream(stream))))
+
+
+class SharedBuffer:
+    """Device memory of this process that other processes can map
+    (oxgpu_b200_shared_alloc), viewable as a torch tensor without a copy."""
+
+    def __init__(self, nbytes: int, device: torch.device | int | None = None):
+        self.device = torch.device("cuda", torch.cuda.current_device() if device is None else
+                                   (device if isinstance(device, int) else device.index))
+        self.nbytes = nbytes
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            check(lib().oxgpu_b200_shared_alloc(nbytes, ctypes.byref(ptr), handle))
+        self.ptr = ptr.value
+        self.handle = handle.raw
+
+    def tensor(self, shape, dtype=torch.float32) -> torch.Tensor:
+        holder = type("_CudaArray", (), {})()
+        holder.__cuda_array_interface__ = {
+            "shape": tuple(shape), "typestr": {torch.float32: "<f4", torch.uint8: "|u1"}[dtype],
+            "data": (self.ptr, False), "version": 2}
+        t = torch.as_tensor(holder, device=self.device)
+        t._oxgpu_keepalive = self
+        return t
+
+    def free(self) -> None:
+        if self.ptr:
+            check(lib().oxgpu_b200_shared_free(ctypes.c_void_p(self.ptr)))
+            self.ptr = 0
+
+
+def shared_open(handle: bytes) -> int:
+    """Map another process's SharedBuffer; returns the address in this process."""
+    ptr = ctypes.c_void_p()
+    check(lib().oxgpu_b200_shared_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def shared_close(ptr: int) -> None:
+    check(lib().oxgpu_b200_shared_close(ctypes.c_void_p(ptr)))
+
+
 def gemm_bf16_out16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
                     stream=None) -> torch.Tensor:
     """bf16 A[M,K], B^T[N,K] -> bf16 C[M,N] (f32 accumulation, one RNE rounding at

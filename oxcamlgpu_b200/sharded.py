@@ -6,10 +6,14 @@ rows [n0, n1) of B^T, a replica of A, and produces the [M, n1-n0] shard of C.
 The reference has no multi-GPU code; the single-GPU call each rank makes is the
 same C-ABI entry point as everywhere else.
 
-An all-gather of C (NCCL over NVLink when the process group is NCCL) is
-optional and separate from the GEMM: NCCL gathers contiguous chunks, so the
-gathered buffer is block-column-major [world][M][N/world]; blocks_to_row_major
-re-interleaves it into C[M,N] when a row-major replica is wanted.
+A replicated C is optional and comes two ways.  all_gather_c is the plain one:
+a separate NCCL all-gather after the GEMM; NCCL gathers contiguous chunks, so
+the gathered buffer is block-column-major [world][M][N/world] and
+blocks_to_row_major re-interleaves it into C[M,N] when a row-major replica is
+wanted.  FusedGatherGemm is the fused one: every rank holds a full row-major
+C[M,N] that the other ranks have mapped, and each rank's GEMM kernel stores
+its tiles into all replicas as they are produced (fan-out epilogue), so the
+transfer over NVLink overlaps the main loop and no re-interleave pass exists.
 """
 from __future__ import annotations
 
@@ -87,3 +91,69 @@ class ColumnShardedGemm:
             raise ValueError("all_gather needs equal shard widths")
         g = all_gather_c(c_shard, self.group)
         return blocks_to_row_major(g) if row_major else g
+
+
+class FusedGatherGemm:
+    """Column-sharded GEMM whose result is replicated on every rank by the GEMM
+    kernel itself: rank r computes C[:, n0:n1] and its epilogue writes each tile
+    to column window [n0, n1) of every rank's row-major C[M,N] (its own by local
+    stores, the others' over NVLink by plain TMA tile stores into memory mapped
+    from the owning process).  No collective runs on the data path; the only
+    exchange is of 64-byte memory handles at construction (any backend).
+
+    run() launches and returns immediately; finish() waits for this rank's
+    kernel and then for every other rank's (a host barrier), after which
+    self.c holds the complete product on every rank."""
+
+    def __init__(self, m: int, n: int, k: int, group=None, flags: int = 0, device=None):
+        from . import gemm
+        self._gemm = gemm
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if self.world > 8:
+            raise ValueError("at most 8 destinations per kernel")
+        self.m, self.n, self.k, self.flags = m, n, k, flags
+        self.parts = column_partition(n, self.world)
+        self.n0, self.n1 = self.parts[self.rank]
+        self.width = self.n1 - self.n0
+        if n % 4:
+            raise ValueError("N must be a multiple of 4 (16-byte aligned column windows)")
+        self._buf = gemm.SharedBuffer(m * n * 4, device)
+        self.c = self._buf.tensor((m, n))
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, self._buf.handle, group=group)
+        self._opened = []
+        self._dest_base = []
+        for r in range(self.world):
+            if r == self.rank:
+                self._dest_base.append(self._buf.ptr)
+            else:
+                ptr = gemm.shared_open(handles[r])
+                self._opened.append(ptr)
+                self._dest_base.append(ptr)
+
+    def run(self, a: torch.Tensor, bt_shard: torch.Tensor) -> None:
+        if tuple(bt_shard.shape) != (self.width, self.k) or tuple(a.shape) != (self.m, self.k):
+            raise ValueError("operand shapes do not match this rank's shard")
+        if self.width == 0:
+            return
+        dests = [base + self.n0 * 4 for base in self._dest_base]
+        self._gemm.gemm_fanout(a, bt_shard, dests, ldc=self.n, flags=self.flags)
+
+    def finish(self) -> torch.Tensor:
+        torch.cuda.current_stream().synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        return self.c
+
+    def close(self) -> None:
+        """Unmap the peers' buffers, then (after a barrier) free this rank's."""
+        for ptr in self._opened:
+            self._gemm.shared_close(ptr)
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.c = None
+        self._buf.free()

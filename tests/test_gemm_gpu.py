@@ -532,6 +532,90 @@ def test_column_shards_concatenate_to_the_unsharded_result(world):
     assert float((whole - exact).abs().max()) <= strict_tol(k, float(a.float().abs().max()), float(bt.float().abs().max()))
 
 
+FANOUT_VARIANTS = ["auto", "1cta_128x128", "2cta_256x256", "2cta_512x256"]
+
+
+@pytest.mark.parametrize("variant", FANOUT_VARIANTS)
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_fanout_epilogue_replicates_the_shards(variant, world):
+    """The fused GEMM + all-gather, all ranks emulated one after the other on one
+    GPU: rank r's kernel writes its column window of every replica.  Each
+    replica must equal the unsharded product of the same variant bit for bit,
+    and nothing outside a window may be touched by the wrong rank."""
+    from oxcamlgpu_b200 import sharded
+    m, n, k = 640, 2304, 320  # 9 column blocks of 256: uneven shard widths for world 2 and 8
+    a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 11, 1.0, 0)
+    gemm.fill_normal(bt, 11, 1.0, m * k)
+    flags = gemm.make_flags(variant)
+    whole = gemm.gemm_bf16(a, bt, flags=flags)
+    replicas = [torch.full((m, n), float("nan"), device=DEV) for _ in range(world)]
+    for n0, n1 in sharded.column_partition(n, world):
+        if n1 > n0:
+            gemm.gemm_fanout(a, bt[n0:n1], [r[:, n0:n1] for r in replicas], flags=flags)
+    for r in replicas:
+        assert torch.equal(r, whole)
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
+    assert float((whole - exact).abs().max()) <= strict_tol(k, float(a.float().abs().max()),
+                                                            float(bt.float().abs().max()))
+
+
+@pytest.mark.parametrize("variant", FANOUT_VARIANTS)
+def test_fanout_ragged_window_does_not_spill(variant):
+    """Ragged M and N: the stores are clipped to each destination's window, so
+    the columns on either side of it keep their contents."""
+    m, n, k = 300, 260, 200
+    rng = np.random.default_rng(5)
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    a, bt = bf16_tensor(a_bits), bf16_tensor(bt_bits)
+    full = [torch.full((m + 3, 1024), -7.0, device=DEV) for _ in range(2)]
+    windows = [f[:m, 256:256 + n] for f in full]
+    gemm.gemm_fanout(a, bt, windows, flags=gemm.make_flags(variant))
+    for f, w in zip(full, windows):
+        check_bf16(a_bits, bt_bits, w)
+        mask = torch.ones_like(f, dtype=torch.bool)
+        mask[:m, 256:256 + n] = False
+        assert bool((f[mask] == -7.0).all())
+
+
+def test_fanout_tf32_and_raw_addresses():
+    m, n, k = 512, 768, 256
+    a = torch.empty(m, k, device=DEV)
+    bt = torch.empty(n, k, device=DEV)
+    gemm.fill_uniform(a, 1, 0)
+    gemm.fill_uniform(bt, 1, m * k)
+    whole = gemm.gemm_tf32(a, bt)
+    full = [torch.zeros(m, 2 * n, device=DEV) for _ in range(3)]
+    gemm.gemm_fanout(a, bt, [f.data_ptr() + n * 4 for f in full], ldc=2 * n)
+    for f in full:
+        assert torch.equal(f[:, n:], whole) and bool((f[:, :n] == 0).all())
+
+
+def test_fanout_rejects_bad_arguments():
+    a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    c = torch.zeros(128, 128, device=DEV)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_fanout(a, a, [c] * 9)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_fanout(a, a, [], ldc=128)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_fanout(a, a, [c], flags=gemm.make_flags("1cta_256x128"))
+    with pytest.raises(OxgpuError):
+        gemm.gemm_fanout(a, a, [c.data_ptr() + 4], ldc=128)
+
+
+def test_shared_buffer_is_a_tensor_view():
+    buf = gemm.SharedBuffer(256 * 4)
+    assert len(buf.handle) == 64
+    t = buf.tensor((16, 16))
+    t.fill_(3.0)
+    torch.cuda.synchronize()
+    assert t.data_ptr() == buf.ptr and float(t.sum()) == 768.0
+    del t
+    buf.free()
+
+
 def test_launch_count_increases():
     before = gemm.launch_count()
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
