@@ -156,6 +156,67 @@ __host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
          ((uint32_t)(umma_m >> 4) << 24);
 }
 
+// Split-K inside a cluster, reduction step: sum one column range of the S
+// partial tiles parked in the S CTAs' shared memory (row r at r * row_bytes,
+// 16-byte pieces XOR-swizzled by r % 8) and write it to C.  Remote loads have a
+// long latency, so each thread keeps 16 of them in flight: UNROLL pieces x S
+// slices, summed in ascending slice order (deterministic).
+struct CrossSliceSum {
+  uint32_t smem_base;       // this CTA's shared-memory address of the parked tile
+  int row_bytes;            // bytes per row of a parked tile
+  int piece0, pieces;       // first 16-byte piece of this CTA's column range, pieces per row (a power of two)
+  int row0, col0;           // tile origin in C
+  float *c;
+  long long ldc;
+  int c_rows, c_cols;
+
+  template <int S>
+  __device__ __forceinline__ void run(int tid, int nthreads) const {
+    constexpr int UNROLL = 16 / S;
+    uint32_t peer[S];
+#pragma unroll
+    for (int s = 0; s < S; s++) peer[s] = ptx::map_to_cta(smem_base, (uint32_t)s);
+    const int total = 128 * pieces, lg = 31 - __clz(pieces);
+    for (int i0 = tid; i0 < total; i0 += nthreads * UNROLL) {
+      float4 v[UNROLL][S];
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++) {
+        const int i = i0 + u * nthreads;
+        const int r = i >> lg, pc = piece0 + (i & (pieces - 1));
+        const uint32_t off = (uint32_t)r * (uint32_t)row_bytes + (((uint32_t)pc ^ (uint32_t)(r & 7)) << 4);
+#pragma unroll
+        for (int s = 0; s < S; s++)
+          if (i < total) v[u][s] = ptx::ld_shared_cluster_v4(peer[s] + off);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; u++) {
+        const int i = i0 + u * nthreads;
+        if (i >= total) break;
+        const int r = i >> lg, pc = piece0 + (i & (pieces - 1));
+        float4 acc = v[u][0];
+#pragma unroll
+        for (int s = 1; s < S; s++) {
+          acc.x += v[u][s].x;
+          acc.y += v[u][s].y;
+          acc.z += v[u][s].z;
+          acc.w += v[u][s].w;
+        }
+        const int row = row0 + r, col = col0 + pc * 4;
+        if (row < c_rows) {
+          float *dst = c + (long long)row * ldc + col;
+          if (col + 4 <= c_cols) {
+            *reinterpret_cast<float4 *>(dst) = acc;
+          } else {
+            const float e[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int q = 0; q < 4; q++)
+              if (col + q < c_cols) dst[q] = e[q];
+          }
+        }
+      }
+    }
+  }
+};
+
 // OUT16: C is stored as bf16 (round to nearest even) instead of f32 -- the
 // narrow-output epilogue the reference lists as future work
 // (docs/roadmap.md:67-71); the C map is then a bf16 map with 64-column boxes.
@@ -608,32 +669,11 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
         const int pieces_per_row = (BN / 4) / S;  // this CTA's column range, in 16-byte pieces
         const int row0 = tm * 128, col0 = tn * BN;
-        uint32_t peer_base[8];
-        for (int s2 = 0; s2 < S && s2 < 8; s2++) peer_base[s2] = ptx::map_to_cta(smem_base, (uint32_t)s2);
-        for (int i = (int)threadIdx.x - 64; i < 128 * pieces_per_row; i += kThreadsPerCta - 64) {
-          const int r = i / pieces_per_row, pj = i - r * pieces_per_row;
-          const int pc = rank * pieces_per_row + pj;
-          const uint32_t off = (uint32_t)r * (uint32_t)(BN * 4) + (((uint32_t)pc ^ (uint32_t)(r & 7)) << 4);
-          float4 acc = ptx::ld_shared_cluster_v4(peer_base[0] + off);
-          for (int s2 = 1; s2 < S; s2++) {  // slices in ascending order: deterministic
-            const float4 v = ptx::ld_shared_cluster_v4(peer_base[s2] + off);
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
-          }
-          const int row = row0 + r, col = col0 + pc * 4;
-          if (row < p.c_rows) {
-            float *dst = p.c_ptr + (long long)row * p.c_ld + col;
-            if (col + 4 <= p.c_cols) {
-              *reinterpret_cast<float4 *>(dst) = acc;
-            } else {
-              const float e[4] = {acc.x, acc.y, acc.z, acc.w};
-              for (int q = 0; q < 4; q++)
-                if (col + q < p.c_cols) dst[q] = e[q];
-            }
-          }
-        }
+        const CrossSliceSum job{smem_base, BN * 4, rank * pieces_per_row, pieces_per_row, row0, col0,
+                                p.c_ptr, p.c_ld, p.c_rows, p.c_cols};
+        if (S == 2) job.template run<2>((int)threadIdx.x - 64, kThreadsPerCta - 64);
+        else if (S == 4) job.template run<4>((int)threadIdx.x - 64, kThreadsPerCta - 64);
+        else job.template run<8>((int)threadIdx.x - 64, kThreadsPerCta - 64);
       }
       ptx::cluster_arrive();
       ptx::cluster_wait();  // nobody retires while a peer may still read its shared memory
