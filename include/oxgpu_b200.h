@@ -190,7 +190,12 @@ enum {
    * few tiles to fill the GPU; OXGPU_FLAG_SPLITS picks the cluster size (2, 4
    * or 8; 0 = chosen by the library). */
   OXGPU_VARIANT_CLUSTER_SPLITK_128x256 = 9,
-  OXGPU_VARIANT_CLUSTER_SPLITK_128x128 = 10
+  OXGPU_VARIANT_CLUSTER_SPLITK_128x128 = 10,
+  /* CTA pair, 256 x 512 per pair: two UMMA 256x256 per K step sharing the staged
+   * A rows; each CTA stages 128 rows of A and 256 contiguous rows of B^T.  The
+   * tile that serves the reference's 128 x 256 catalog boxes with pair-tile
+   * operand traffic. */
+  OXGPU_VARIANT_2CTA_256x512 = 11
 };
 #define OXGPU_FLAG_VARIANT(v) ((unsigned)(v) & 0xffu)
 #define OXGPU_FLAG_STAGES(s) (((unsigned)(s) & 0xfu) << 8)    /* 0 = deepest that fits */

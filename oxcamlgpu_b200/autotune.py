@@ -21,7 +21,7 @@ import torch
 
 from . import catalog, gemm
 
-BUFFER_VARIANTS = ("2cta_512x256", "2cta_256x256", "2cta_256x128", "1cta_256x256", "1cta_128x256",
+BUFFER_VARIANTS = ("2cta_512x256", "2cta_256x512", "2cta_256x256", "2cta_256x128", "1cta_256x256", "1cta_128x256",
                    "1cta_256x128", "1cta_128x128")
 
 

@@ -23,7 +23,7 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kKinds = 5;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out
-constexpr int kVariants = 11;  // index by Variant value
+constexpr int kVariants = 12;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
 
@@ -146,6 +146,7 @@ const void *kernel_for(int kind, int variant, bool out16 = false) {
       case VARIANT_2CTA_256x128: return OX_K(0, 128, 128, 2);
       case VARIANT_2CTA_512x256: return OX_K(0, 256, 256, 2);
       case VARIANT_1CTA_256x256: return OX_K(0, 256, 256, 1);
+      case VARIANT_2CTA_256x512: return (const void *)umma_gemm_kernel<0, 128, 256, 2, false, false, 2>;
     }
   } else {
     switch (variant) {
@@ -156,6 +157,7 @@ const void *kernel_for(int kind, int variant, bool out16 = false) {
       case VARIANT_2CTA_256x128: return OX_K(1, 128, 128, 2);
       case VARIANT_2CTA_512x256: return OX_K(1, 256, 256, 2);
       case VARIANT_1CTA_256x256: return OX_K(1, 256, 256, 1);
+      case VARIANT_2CTA_256x512: return (const void *)umma_gemm_kernel<1, 128, 256, 2, false, false, 2>;
     }
   }
 #undef OX_K
@@ -657,15 +659,20 @@ int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uin
                   t.bn, t.bk);
     return fail(OXGPU_E_SHAPE, text);
   }
-  // Every catalog box (64, 128 or 256 rows) divides a 256 x 256 tile, so when
-  // M and N allow it the entry is served by the one-CTA 256x256 kernel (two
-  // UMMA 128x256 sharing the staged B^T rows: 64 instead of 96 bytes of operand
-  // traffic per clock at full rate; 0.91 instead of 0.79 of cuBLAS at bf16
-  // 8192^3 with the reference's own maps).  Otherwise the entry's own tile
-  // shape is used.  A CTA-pair tile is out of reach here: each CTA of a pair
-  // stages half of the B^T rows, and the caller's box cannot be halved.
+  // The caller's maps fix the rows one load brings (the entry's bm rows of A,
+  // bn rows of B^T); any tile whose per-CTA rows are multiples of those boxes
+  // can serve the entry.  In order of operand traffic per flop:
+  //  * 64/128-row A box: the CTA pair with two 256-column blocks (256 x 512 per
+  //    pair): each CTA stages 128 rows of A and 256 CONTIGUOUS rows of B^T, which
+  //    the reference's 256-row B^T box delivers in one load (48 bytes of operand
+  //    per clock per SM at full rate, as the library's own 512 x 256 tile);
+  //  * 256-row A box with a 128-row B^T box: the 512 x 256 pair tile as is;
+  //  * otherwise the one-CTA 256 x 256 tile (64 bytes per clock), and the
+  //    entry's own tile shape when M or N is not a multiple of 256.
   int variant = e->variant;
-  if (m % 256 == 0 && n % 256 == 0) variant = VARIANT_1CTA_256x256;
+  if (t.bm <= 128 && m % 256 == 0 && n % 512 == 0) variant = VARIANT_2CTA_256x512;
+  else if (t.bm == 256 && t.bn == 128 && m % 512 == 0 && n % 256 == 0) variant = VARIANT_2CTA_512x256;
+  else if (m % 256 == 0 && n % 256 == 0) variant = VARIANT_1CTA_256x256;
   const VariantShape shape = variant_shape(variant);
   if (m % shape.tile_m)
     return fail(OXGPU_E_SHAPE, "this entry is served by a 128-row tcgen05 tile: M must be a multiple of 128");

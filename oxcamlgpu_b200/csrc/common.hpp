@@ -30,6 +30,7 @@ enum Variant {
   VARIANT_1CTA_256x256 = 8,
   VARIANT_CLUSTER_SPLITK_128x256 = 9,   // K slices across a cluster, reduced through DSMEM
   VARIANT_CLUSTER_SPLITK_128x128 = 10,
+  VARIANT_2CTA_256x512 = 11,            // two 256-column blocks per pair tile; each CTA stages 256 contiguous B^T rows
 };
 
 // Every tcgen05 GEMM kernel here runs 10 warps: TMA producer, MMA issuer (also
@@ -69,6 +70,7 @@ inline VariantShape variant_shape(int variant) {
     case VARIANT_2CTA_256x128: return {2, 256, 128, 128, 64};
     case VARIANT_2CTA_512x256: return {2, 512, 256, 256, 128};
     case VARIANT_1CTA_256x256: return {1, 256, 256, 256, 256};
+    case VARIANT_2CTA_256x512: return {2, 256, 512, 128, 256};
     default: return {0, 0, 0, 0, 0};
   }
 }

@@ -220,7 +220,12 @@ struct CrossSliceSum {
 // OUT16: C is stored as bf16 (round to nearest even) instead of f32 -- the
 // narrow-output epilogue the reference lists as future work
 // (docs/roadmap.md:67-71); the C map is then a bf16 map with 64-column boxes.
-template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false>
+// NI: column blocks of BN per tile (tile width NI * BN).  NI == 2 exists for
+// CTA pairs whose CTAs each stage 2 * BN / 2 CONTIGUOUS rows of B^T in one box
+// (the reference's 256-row B^T box): UMMA `ni` of a K step reads rows
+// [ni * BN/2, (ni + 1) * BN/2) of both CTAs' stages, so accumulator column j of
+// block ni is tile column (j / (BN/2)) * BN + ni * BN/2 + j % (BN/2).
+template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
 umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmParamsFanout, GemmParams>::type p) {
   static_assert(!(FANOUT && OUT16), "the fan-out epilogue writes f32");
@@ -228,22 +233,24 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   // per K step, all sharing the staged B^T rows).  Block `mi` of accumulator
   // set `set` is one hand-off unit between the issuer and the epilogue.
   constexpr int MI = BM_CTA / 128;
+  constexpr int U = MI * NI;                      // hand-off units (UMMA blocks) per accumulator set
   constexpr int UMMA_M = 128 * CTA_GROUP;         // rows one instruction produces (per pair)
-  constexpr int B_ROWS = BN / CTA_GROUP;          // rows of B^T this CTA stages
-  constexpr int ACC_COLS = MI * BN;               // TMEM columns of one accumulator set
+  constexpr int B_ROWS = BN / CTA_GROUP;          // rows of B^T this CTA stages per column block
+  constexpr int ACC_COLS = U * BN;                // TMEM columns of one accumulator set
   constexpr int SETS = (2 * ACC_COLS <= 512) ? 2 : 1;  // two sets: epilogue overlaps next main loop
   constexpr int TMEM_COLS = SETS * ACC_COLS;
   constexpr int CHUNKS = BN / 32;                 // 32-column epilogue chunks per unit
-  // 8 epilogue warps form two groups; with MI == 2 group g drains block mi = g,
-  // with MI == 1 the groups split the unit's columns.
-  constexpr int CHUNKS_PER_GROUP = MI == 2 ? CHUNKS : CHUNKS / 2;
-  constexpr int EMPTY_ARRIVALS = (MI == 2 ? 4 : 8) * CTA_GROUP;
+  // 8 epilogue warps form two groups; with two units group g drains unit g,
+  // with one unit the groups split its columns.
+  constexpr int CHUNKS_PER_GROUP = U == 2 ? CHUNKS : CHUNKS / 2;
+  constexpr int EMPTY_ARRIVALS = (U == 2 ? 4 : 8) * CTA_GROUP;
   constexpr uint32_t A_BYTES = BM_CTA * 128;
-  constexpr uint32_t B_BYTES = B_ROWS * 128;
+  constexpr uint32_t B_BYTES = NI * B_ROWS * 128;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t IDESC = instr_desc<KIND>(UMMA_M, BN);
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
   static_assert(BM_CTA == 128 || BM_CTA == 256, "unsupported tile");
+  static_assert(NI == 1 || (NI == 2 && MI == 1 && CTA_GROUP == 2 && !OUT16), "unsupported column blocking");
   static_assert(CHUNKS_PER_GROUP >= 1 && CHUNKS % 2 == 0, "unsupported tile width");
 
   extern __shared__ uint8_t smem_raw[];
@@ -287,7 +294,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       ptx::mbar_init(full_bar + 8u * s, 1);
       ptx::mbar_init(empty_bar + 8u * s, 1);
     }
-    for (int u = 0; u < SETS * MI; u++) {
+    for (int u = 0; u < SETS * U; u++) {
       ptx::mbar_init(tmem_full_bar + 8u * u, 1);
       // one arrival per epilogue warp (of every CTA feeding this issuer) that reads the unit
       ptx::mbar_init(tmem_empty_bar + 8u * u, EMPTY_ARRIVALS);
@@ -340,7 +347,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         int tm, tn;
         grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
         const int a_row0 = tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA;
-        const int b_row0 = tn * BN + (int)cta_rank * B_ROWS;
+        const int b_row0 = tn * (NI * BN) + (int)cta_rank * (NI * B_ROWS);
         for (int kb = kb_begin; kb < kb_end; kb++) {
           if (!bounded_wait(empty_bar + 8u * stage, phase ^ 1u, wctx, WAIT_EMPTY, (uint32_t)stage)) {
             ok = false;
@@ -354,7 +361,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
             ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
             for (int r = 0; r < BM_CTA; r += p.a_box_rows)
               ptx::tma_load_2d_hint(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar, pol_a);
-            for (int r = 0; r < B_ROWS; r += p.b_box_rows)
+            for (int r = 0; r < NI * B_ROWS; r += p.b_box_rows)
               ptx::tma_load_2d_hint(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar, pol_b);
           } else {
             // Both CTAs credit the leader's barrier; the leader expects the
@@ -363,7 +370,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
             const uint32_t bar = full_remote0 + 8u * stage;
             for (int r = 0; r < BM_CTA; r += p.a_box_rows)
               ptx::tma_load_2d_pair_hint(a_dst + (uint32_t)r * 128u, map_a, kc, a_row0 + r, bar, pol_a);
-            for (int r = 0; r < B_ROWS; r += p.b_box_rows)
+            for (int r = 0; r < NI * B_ROWS; r += p.b_box_rows)
               ptx::tma_load_2d_pair_hint(b_dst + (uint32_t)r * 128u, map_b, kc, b_row0 + r, bar, pol_b);
           }
           issued++;
@@ -400,13 +407,13 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       // row block `mi`, reading ring slot `slot`.  The start address advances
       // inside the swizzle span, as the reference does with its `+8*ki` /
       // `+16*ki` element offsets (gemm.ml:121-125).
-      auto issue = [&](int slot, int mi, uint32_t d_tmem, bool first_block) {
+      auto issue = [&](int slot, int u, uint32_t d_tmem, bool first_block) {
         const uint32_t a_addr = smem_base + (uint32_t)slot * STAGE_BYTES;
-        const uint64_t a_desc = smem_desc_sw128(a_addr) + (uint64_t)((mi * 128 * 128) >> 4);
-        const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES);
+        const uint64_t a_desc = smem_desc_sw128(a_addr) + (uint64_t)(((MI == 2 ? u : 0) * 128 * 128) >> 4);
+        const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES) + (uint64_t)(((NI == 2 ? u : 0) * B_ROWS * 128) >> 4);
 #pragma unroll
         for (int ki = 0; ki < 4; ki++)
-          ptx::umma<KIND, CTA_GROUP>(d_tmem + (uint32_t)(mi * BN), a_desc + (uint64_t)(ki * 2),
+          ptx::umma<KIND, CTA_GROUP>(d_tmem + (uint32_t)(u * BN), a_desc + (uint64_t)(ki * 2),
                                      b_desc + (uint64_t)(ki * 2), IDESC, (!first_block || ki > 0) ? 1u : 0u);
       };
       auto release_slot = [&](int slot) {  // frees the ring slot once the UMMAs issued so far have read it
@@ -441,7 +448,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         // block 1 is still being drained.  The G slots involved stay occupied
         // until the second pass has read them.
         int G = 0;
-        if constexpr (MI == 2) {
+        if constexpr (U == 2) {
           G = p.reorder_kb;
           if (G > stages - 1) G = stages - 1;
           if (G > (kb_end - kb_begin) / 2) G = (kb_end - kb_begin) / 2;
@@ -449,14 +456,14 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         int kb = kb_begin;
         if (G > 0) {
           // ---- head, row block 0 then row block 1 ----
-          ok = bounded_wait(tmem_empty_bar + 8u * (set * MI), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
+          ok = bounded_wait(tmem_empty_bar + 8u * (set * U), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
           for (int i = 0; ok && i < G; i++) {
             ok = bounded_wait(full_bar + 8u * slot_of(i), phase_of(i), wctx, WAIT_FULL, (uint32_t)slot_of(i));
             if (!ok) break;
             ptx::tc_fence_after_sync();
             issue(slot_of(i), 0, d_tmem, i == 0);
           }
-          if (ok) ok = bounded_wait(tmem_empty_bar + 8u * (set * MI + 1), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
+          if (ok) ok = bounded_wait(tmem_empty_bar + 8u * (set * U + 1), set_phase ^ 1u, wctx, WAIT_TMEM_EMPTY, (uint32_t)w);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           for (int i = 0; i < G; i++) {
@@ -466,8 +473,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           }
           kb += G;
         } else {
-          for (int mi = 0; ok && mi < MI; mi++)
-            ok = bounded_wait(tmem_empty_bar + 8u * (set * MI + mi), set_phase ^ 1u, wctx,
+          for (int mi = 0; ok && mi < U; mi++)
+            ok = bounded_wait(tmem_empty_bar + 8u * (set * U + mi), set_phase ^ 1u, wctx,
                               WAIT_TMEM_EMPTY, (uint32_t)w);
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -480,7 +487,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           }
           ptx::tc_fence_after_sync();
 #pragma unroll
-          for (int mi = 0; mi < MI; mi++) issue(stage, mi, d_tmem, kb == kb_begin);
+          for (int mi = 0; mi < U; mi++) issue(stage, mi, d_tmem, kb == kb_begin);
           release_slot(stage);
           advance();
         }
@@ -494,15 +501,15 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
             issue(slot_of(i), 0, d_tmem, false);
           }
           if (!ok) break;
-          publish(set * MI);
+          publish(set * U);
           for (int i = 0; i < G; i++) {
             issue(stage, 1, d_tmem, false);
             release_slot(stage);
             advance();
           }
-          publish(set * MI + 1);
+          publish(set * U + 1);
         } else {
-          for (int mi = 0; mi < MI; mi++) publish(set * MI + mi);
+          for (int mi = 0; mi < U; mi++) publish(set * U + mi);
         }
       }
       if (!ok || *abort_ptr) {
@@ -519,8 +526,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     const int quad = warp & 3;         // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     const int ew = warp - 2;           // 0..7, staging slot
     const int group = ew >> 2;         // 0 or 1
-    const int mi = MI == 2 ? group : 0;
-    const int ch_begin = MI == 2 ? 0 : group * CHUNKS_PER_GROUP;
+    const int mi = U == 2 ? group : 0;  // the unit this warp drains
+    const int ch_begin = U == 2 ? 0 : group * CHUNKS_PER_GROUP;
     const uint32_t buf = staging_base + (uint32_t)ew * 4096u;  // one 32x32 f32 sub-tile
     const uint32_t row_addr = buf + (uint32_t)lane * 128u;
     const uint32_t tmem_empty_remote =
@@ -533,12 +540,17 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       const int t = w / p.splits, sp = w - t * p.splits;
       const int set = local_tile % SETS;
       const uint32_t set_phase = (uint32_t)(local_tile / SETS) & 1u;
-      const int unit = set * MI + mi;
+      const int unit = set * U + mi;
       int tm, tn;
       grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
       const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
-                        mi * 128 + quad * 32;
-      const int c_col0 = tn * BN + ch_begin * 32;
+                        (MI == 2 ? mi * 128 : 0) + quad * 32;
+      // first column in C of this warp's chunk c (32 accumulator columns)
+      auto chunk_col = [&](int c) {
+        const int j = (ch_begin + c) * 32;
+        if constexpr (NI == 1) return tn * BN + j;
+        else return tn * (NI * BN) + (j / B_ROWS) * (NI * B_ROWS) + mi * B_ROWS + j % B_ROWS;
+      };
       // one lane waits (the wait can last a whole main loop); the rest of the
       // warp parks at the shuffle instead of polling the barrier
       uint32_t got = 0;
@@ -611,9 +623,9 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
               // one bulk group per sub-tile: the staging buffer is reused once
               // every destination's store has read it
               for (int d = 0; d < p.n_dests; d++)
-                ptx::tma_store_2d_hint(&p.dest_maps[d], c_col0 + c * 32, c_row, buf, pol_c);
+                ptx::tma_store_2d_hint(&p.dest_maps[d], chunk_col(c), c_row, buf, pol_c);
             } else {
-              ptx::tma_store_2d_hint(map_c, c_col0 + c * 32, c_row, buf, pol_c);
+              ptx::tma_store_2d_hint(map_c, chunk_col(c), c_row, buf, pol_c);
             }
             ptx::tma_store_commit();
           }
@@ -641,7 +653,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d_hint(map_c, c_col0 + c2 * 64, c_row, buf, pol_c);
+            ptx::tma_store_2d_hint(map_c, chunk_col(2 * c2), c_row, buf, pol_c);
             ptx::tma_store_commit();
           }
         }

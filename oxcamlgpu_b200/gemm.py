@@ -16,12 +16,13 @@ from . import catalog
 from ._lib import check, lib
 
 (VARIANT_AUTO, V_1CTA_128x256, V_1CTA_128x128, V_1CTA_256x128, V_2CTA_256x256, V_2CTA_256x128, V_SPLITK,
- V_2CTA_512x256, V_1CTA_256x256, V_CSPLITK_128x256, V_CSPLITK_128x128) = range(11)
+ V_2CTA_512x256, V_1CTA_256x256, V_CSPLITK_128x256, V_CSPLITK_128x128, V_2CTA_256x512) = range(12)
 VARIANT_NAMES = {
     "auto": VARIANT_AUTO, "1cta_128x256": V_1CTA_128x256, "1cta_128x128": V_1CTA_128x128,
     "1cta_256x128": V_1CTA_256x128, "2cta_256x256": V_2CTA_256x256, "2cta_256x128": V_2CTA_256x128,
     "splitk": V_SPLITK, "2cta_512x256": V_2CTA_512x256, "1cta_256x256": V_1CTA_256x256,
     "cluster_splitk_128x256": V_CSPLITK_128x256, "cluster_splitk_128x128": V_CSPLITK_128x128,
+    "2cta_256x512": V_2CTA_256x512,
 }
 ELEMENT_BYTES = {"f32": 4, "bf16": 2}
 INPUT_NONE, INPUT_TF32, INPUT_BF16 = 0, 1, 2

@@ -32,7 +32,7 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 TC_VARIANTS = ["1cta_128x256", "1cta_128x128", "1cta_256x128", "2cta_256x256", "2cta_256x128", "2cta_512x256",
-               "1cta_256x256"]
+               "1cta_256x256", "2cta_256x512"]
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -142,11 +142,13 @@ def test_pattern_case_through_catalog_entry(golden_dir, name, fixture, k, narrow
     assert rel.max() <= 2.0 ** -16, rel.max()
 
 
-@pytest.mark.parametrize("mn", [(512, 512), (384, 768), (512, 384)])
+@pytest.mark.parametrize("mn", [(512, 512), (1024, 1536), (768, 768), (384, 768), (512, 384)])
 @pytest.mark.parametrize("name", cat.ENTRY_NAMES)
 def test_every_catalog_entry(name, mn):
-    """(512, 512) is served by the 256x256 kernel (every box divides it); the
-    other sizes fall back to the entry's own tile shape."""
+    """(512, 512) and (1024, 1536) are served by a CTA-pair tile (256x512 for the
+    64/128-row A boxes, 512x256 for the 256-row ones), (768, 768) by the one-CTA
+    256x256 kernel (every box divides it); the other sizes fall back to the
+    entry's own tile shape."""
     tile, eb = cat.kernel_tile(name)
     rng = np.random.default_rng(len(name) * 31 + mn[0])
     m, n, k = mn[0], mn[1], 5 * tile.bk
@@ -233,7 +235,7 @@ def test_ring_and_parity_sweep_bf16(variant, kblocks):
         check_bf16(a_bits, bt_bits, c)
 
 
-@pytest.mark.parametrize("variant", ["1cta_256x128", "2cta_512x256", "1cta_256x256"])
+@pytest.mark.parametrize("variant", ["1cta_256x128", "2cta_512x256", "1cta_256x256", "2cta_256x512"])
 @pytest.mark.parametrize("reorder", [15, 1, 2, 3])
 @pytest.mark.parametrize("kblocks", [1, 2, 3, 5, 6, 7, 12])
 def test_block_major_tile_ends(variant, reorder, kblocks):
