@@ -27,7 +27,11 @@ BUFFER_VARIANTS = ("2cta_512x256", "2cta_256x512", "2cta_256x256", "2cta_256x128
 
 def candidates(m: int, n: int, k: int, element: str):
     """(label, callable factory) pairs valid for this size."""
-    out = []
+    out = [("auto (library default)", dict(variant="auto"))]
+    if k >= 2048 and m <= 512:
+        for v, splits in (("cluster_splitk_128x256", 4), ("cluster_splitk_128x256", 2),
+                          ("cluster_splitk_128x128", 2), ("cluster_splitk_128x128", 4)):
+            out.append((f"{v},splits={splits}", dict(variant=v, splits=splits)))
     for v in BUFFER_VARIANTS:
         for group in (8, 16):
             out.append((f"{v},group_m={group}", dict(variant=v, group_m=group)))

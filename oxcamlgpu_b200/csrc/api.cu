@@ -669,16 +669,22 @@ int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uin
   //  * 256-row A box with a 128-row B^T box: the 512 x 256 pair tile as is;
   //  * otherwise the one-CTA 256 x 256 tile (64 bytes per clock), and the
   //    entry's own tile shape when M or N is not a multiple of 256.
-  int variant = e->variant;
-  if (t.bm <= 128 && m % 256 == 0 && n % 512 == 0) variant = VARIANT_2CTA_256x512;
-  else if (t.bm == 256 && t.bn == 128 && m % 512 == 0 && n % 256 == 0) variant = VARIANT_2CTA_512x256;
-  else if (m % 256 == 0 && n % 256 == 0) variant = VARIANT_1CTA_256x256;
-  const VariantShape shape = variant_shape(variant);
-  if (m % shape.tile_m)
+  // A larger tile is only taken when it still gives every SM (or SM pair) a
+  // tile; small problems keep the entry's own shape so more SMs have work.
+  if (m % variant_shape(e->variant).tile_m)
     return fail(OXGPU_E_SHAPE, "this entry is served by a 128-row tcgen05 tile: M must be a multiple of 128");
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
+  const long long pairs = dev->sm_count / 2;
+  auto tiles = [&](int tm, int tn) { return (long long)(m / tm) * (n / tn); };
+  int variant = e->variant;
+  if (t.bm <= 128 && m % 256 == 0 && n % 512 == 0 && tiles(256, 512) >= pairs)
+    variant = VARIANT_2CTA_256x512;
+  else if (t.bm == 256 && t.bn == 128 && m % 512 == 0 && n % 256 == 0 && tiles(512, 256) >= pairs)
+    variant = VARIANT_2CTA_512x256;
+  else if (m % 256 == 0 && n % 256 == 0 && tiles(256, 256) >= dev->sm_count)
+    variant = VARIANT_1CTA_256x256;
   GemmParams p;
   std::memset(&p, 0, sizeof p);
   p.a_map_ptr = (const void *)(uintptr_t)a_tmap;

@@ -142,13 +142,13 @@ def test_pattern_case_through_catalog_entry(golden_dir, name, fixture, k, narrow
     assert rel.max() <= 2.0 ** -16, rel.max()
 
 
-@pytest.mark.parametrize("mn", [(512, 512), (1024, 1536), (768, 768), (384, 768), (512, 384)])
+@pytest.mark.parametrize("mn", [(512, 512), (2560, 4096), (2560, 4352), (384, 768), (512, 384)])
 @pytest.mark.parametrize("name", cat.ENTRY_NAMES)
 def test_every_catalog_entry(name, mn):
-    """(512, 512) and (1024, 1536) are served by a CTA-pair tile (256x512 for the
-    64/128-row A boxes, 512x256 for the 256-row ones), (768, 768) by the one-CTA
-    256x256 kernel (every box divides it); the other sizes fall back to the
-    entry's own tile shape."""
+    """(2560, 4096) has enough tiles for a CTA-pair tile (256x512 for the 64/128-row
+    A boxes, 512x256 for the 256-row ones), (2560, 4352) for the one-CTA 256x256
+    kernel (every box divides it); the small sizes keep the entry's own tile
+    shape."""
     tile, eb = cat.kernel_tile(name)
     rng = np.random.default_rng(len(name) * 31 + mn[0])
     m, n, k = mn[0], mn[1], 5 * tile.bk
