@@ -237,6 +237,32 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
                                       unsigned flags, void *workspace, size_t workspace_bytes,
                                       void *stream);
 
+/* GEMM with an affine epilogue: C = alpha * (A B) + beta * C_in + bias, applied to
+ * the accumulator on its way from TMEM to the store (the fused epilogue beyond
+ * the reference's plain overwrite, examples/kernels/gemm.ml:143-161; its
+ * roadmap lists only the narrow output, docs/roadmap.md:67-71).  bias: f32 [N],
+ * broadcast over rows, 16-byte aligned, or NULL.  c_in: f32 [M,N] with leading
+ * dimension ldc_in, read only when beta != 0 (so it may hold anything, NaN
+ * included, when beta == 0); it may be C itself for an in-place update.  Each of
+ * the three steps rounds to f32 on its own, in this order:
+ * (alpha * acc + beta * c_in) + bias.  Same operand contracts and flags as
+ * oxgpu_b200_gemm_bf16 / _tf32; variants: auto, 1CTA_128x128, 2CTA_256x256,
+ * 2CTA_512x256. */
+typedef struct oxgpu_epilogue {
+  float alpha, beta;
+  const float *bias;
+  const float *c_in;
+  int64_t ldc_in;
+} oxgpu_epilogue;
+OXGPU_API int oxgpu_b200_gemm_bf16_affine(const uint16_t *a, const uint16_t *bt, float *c, int m,
+                                          int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                          const oxgpu_epilogue *epilogue, unsigned flags,
+                                          void *stream);
+OXGPU_API int oxgpu_b200_gemm_tf32_affine(const float *a, const float *bt, float *c, int m, int n,
+                                          int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                          const oxgpu_epilogue *epilogue, unsigned flags,
+                                          void *stream);
+
 /* GEMM with a fan-out epilogue: every tile of C is written to n_dests (1..8)
  * destinations as it leaves the tensor cores.  (No counterpart in the reference,
  * which has no multi-GPU path; this is the "GEMM, then all-gather of the column

@@ -30,6 +30,11 @@ class GpuHeaderStruct(ctypes.Structure):
                 ("args", GpuSlotStruct * 16), ("result", GpuSlotStruct)]
 
 
+class EpilogueStruct(ctypes.Structure):
+    _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("bias", ctypes.c_void_p),
+                ("c_in", ctypes.c_void_p), ("ldc_in", ctypes.c_int64)]
+
+
 class TileConfigStruct(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("bm", "bn", "bk", "stages", "producers")]
 
@@ -79,6 +84,10 @@ def lib() -> ctypes.CDLL:
                                          c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_gemm_tf32_fanout": ([c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int,
                                          c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_gemm_bf16_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
+                                         ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_gemm_tf32_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
+                                         ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_shared_alloc": ([sz, ctypes.POINTER(c_void_p), ctypes.c_char_p], c_int),
         "oxgpu_b200_shared_open": ([ctypes.c_char_p, ctypes.POINTER(c_void_p)], c_int),
         "oxgpu_b200_shared_close": ([c_void_p], c_int),

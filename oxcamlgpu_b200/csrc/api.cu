@@ -22,7 +22,7 @@ namespace oxgpu {
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kKinds = 5;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out
+constexpr int kKinds = 7;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out, 5 / 6 = affine
 constexpr int kVariants = 12;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
@@ -184,6 +184,26 @@ const void *fanout_kernel_for(int kind, int variant) {
   return nullptr;
 }
 
+// Kernels with the affine epilogue (alpha, beta, bias).
+const void *affine_kernel_for(int kind, int variant) {
+#define OX_A(K, BM, BN, CG) ((const void *)umma_gemm_kernel<K, BM, BN, CG, false, false, 1, true>)
+  if (kind == 0) {
+    switch (variant) {
+      case VARIANT_1CTA_128x128: return OX_A(0, 128, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_A(0, 128, 256, 2);
+      case VARIANT_2CTA_512x256: return OX_A(0, 256, 256, 2);
+    }
+  } else {
+    switch (variant) {
+      case VARIANT_1CTA_128x128: return OX_A(1, 128, 128, 1);
+      case VARIANT_2CTA_256x256: return OX_A(1, 128, 256, 2);
+      case VARIANT_2CTA_512x256: return OX_A(1, 256, 256, 2);
+    }
+  }
+#undef OX_A
+  return nullptr;
+}
+
 unsigned long long wait_budget_ns() {
   static unsigned long long v = [] {
     const char *e = std::getenv("OXGPU_WAIT_BUDGET_MS");
@@ -201,6 +221,7 @@ struct LaunchPlan {
   bool out16 = false;   // bf16 C
   int cluster_splits = 0;  // > 1: split-K across a cluster of that many CTAs (one-CTA 128-row tiles)
   bool fanout = false;     // `p` is a GemmParamsFanout and the fan-out kernel is launched
+  bool affine = false;     // the kernel with the affine epilogue is launched
 };
 
 // K blocks issued block-major at either end of a tile (two-row-block tiles).
@@ -211,10 +232,11 @@ constexpr int kDefaultReorderKb = 3;
 int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, int n, int k,
                 cudaStream_t stream) {
   const VariantShape shape = variant_shape(plan.variant);
-  const void *fn = plan.fanout ? fanout_kernel_for(plan.kind, plan.variant)
-                               : kernel_for(plan.kind, plan.variant, plan.out16);
+  const void *fn = plan.fanout   ? fanout_kernel_for(plan.kind, plan.variant)
+                   : plan.affine ? affine_kernel_for(plan.kind, plan.variant)
+                                 : kernel_for(plan.kind, plan.variant, plan.out16);
   if (!fn || shape.cta_group == 0) return fail(OXGPU_E_INVALID_ARG, "unknown kernel variant");
-  const int attr_kind = plan.fanout ? 3 + plan.kind : (plan.out16 ? 2 : plan.kind);
+  const int attr_kind = plan.fanout ? 3 + plan.kind : plan.affine ? 5 + plan.kind : (plan.out16 ? 2 : plan.kind);
   int stages = plan.stages;
   const int most = variant_max_stages(plan.variant);
   if (stages <= 0 || stages > most) stages = most;
@@ -464,6 +486,15 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   return OXGPU_OK;
 }
 
+// The three tile shapes the fan-out and affine kernels exist for.
+int choose_large_tile_variant(const DeviceState &dev, int m, int n) {
+  auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
+  const int pairs = dev.sm_count / 2;
+  return tiles(512, 256) >= pairs   ? VARIANT_2CTA_512x256
+         : tiles(256, 256) >= pairs ? VARIANT_2CTA_256x256
+                                    : VARIANT_1CTA_128x128;
+}
+
 // GEMM whose C tiles go to several destinations (see GemmParamsFanout).
 int gemm_fanout(int kind, const void *a, const void *bt, float *const *dests, int n_dests, int m, int n,
                 int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags, cudaStream_t stream) {
@@ -478,13 +509,7 @@ int gemm_fanout(int kind, const void *a, const void *bt, float *const *dests, in
   if ((st = current_device(&dev_index, &dev))) return st;
 
   int variant = (int)(flags & 0xffu);
-  if (variant == VARIANT_AUTO) {
-    auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
-    const int pairs = dev->sm_count / 2;
-    variant = tiles(512, 256) >= pairs   ? VARIANT_2CTA_512x256
-              : tiles(256, 256) >= pairs ? VARIANT_2CTA_256x256
-                                         : VARIANT_1CTA_128x128;
-  }
+  if (variant == VARIANT_AUTO) variant = choose_large_tile_variant(*dev, m, n);
   if (!fanout_kernel_for(kind, variant))
     return fail(OXGPU_E_INVALID_ARG, "this variant has no fan-out kernel (use 1cta_128x128, 2cta_256x256 or 2cta_512x256)");
   const VariantShape shape = variant_shape(variant);
@@ -506,6 +531,53 @@ int gemm_fanout(int kind, const void *a, const void *bt, float *const *dests, in
     if ((st = encode_2d(&p.dest_maps[d], dests[d], 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32)))
       return st;
   p.n_dests = n_dests;
+  return launch_umma(*dev, plan, p, m, n, k, stream);
+}
+
+// C = alpha * (A B) + beta * C_in + bias in the GEMM's own epilogue.
+int gemm_affine(int kind, const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
+                int64_t ldb, int64_t ldc, const oxgpu_epilogue *ep, unsigned flags, cudaStream_t stream) {
+  const int esize = kind == 0 ? 2 : 4;
+  if (!ep) return fail(OXGPU_E_INVALID_ARG, "null epilogue description");
+  int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, esize);
+  if (st) return st;
+  if (ep->bias && !aligned16(ep->bias)) return fail(OXGPU_E_ALIGN, "bias must be 16-byte aligned");
+  if (ep->beta != 0.0f) {
+    if (!ep->c_in) return fail(OXGPU_E_INVALID_ARG, "beta != 0 needs c_in");
+    if (!aligned16(ep->c_in) || (ep->ldc_in * 4) % 16 || ep->ldc_in < n)
+      return fail(OXGPU_E_ALIGN, "c_in must be 16-byte aligned with a leading dimension that is a multiple of 4 and at least N");
+  }
+  int dev_index;
+  DeviceState *dev = nullptr;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  int variant = (int)(flags & 0xffu);
+  if (variant == VARIANT_AUTO) variant = choose_large_tile_variant(*dev, m, n);
+  if (!affine_kernel_for(kind, variant))
+    return fail(OXGPU_E_INVALID_ARG, "this variant has no affine-epilogue kernel (use 1cta_128x128, 2cta_256x256 or 2cta_512x256)");
+  const VariantShape shape = variant_shape(variant);
+  const int kbe = kind == 0 ? 64 : 32;
+  LaunchPlan plan{kind, variant, (int)((flags >> 8) & 0xfu), (int)((flags >> 12) & 0xffu), 1, 0, 0};
+  const int reorder_field = (int)((flags >> 28) & 0xfu);
+  plan.reorder_kb = reorder_field == 0 ? -1 : (reorder_field == 15 ? 0 : reorder_field);
+  plan.affine = true;
+  GemmParams p;
+  std::memset(&p, 0, sizeof p);
+  p.a_box_rows = shape.cta_a_rows;
+  p.b_box_rows = shape.cta_b_rows;
+  if ((st = encode_2d(&p.map_a, a, esize, (uint64_t)k, (uint64_t)m, (uint64_t)lda * esize, kbe, p.a_box_rows)))
+    return st;
+  if ((st = encode_2d(&p.map_b, bt, esize, (uint64_t)k, (uint64_t)n, (uint64_t)ldb * esize, kbe, p.b_box_rows)))
+    return st;
+  if ((st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32))) return st;
+  p.c_ptr = c;
+  p.c_ld = ldc;
+  p.c_rows = m;
+  p.c_cols = n;
+  p.alpha = ep->alpha;
+  p.beta = ep->beta;
+  p.bias = ep->bias;
+  p.c_in = ep->beta != 0.0f ? ep->c_in : nullptr;
+  p.c_in_ld = ep->ldc_in;
   return launch_umma(*dev, plan, p, m, n, k, stream);
 }
 
@@ -749,6 +821,18 @@ int oxgpu_b200_gemm_tf32_fanout(const float *a, const float *bt, float *const *c
                                 int n, int k, int64_t lda, int64_t ldb, int64_t ldc, unsigned flags,
                                 void *stream) {
   return oxgpu::gemm_fanout(1, a, bt, c_dests, n_dests, m, n, k, lda, ldb, ldc, flags, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_bf16_affine(const uint16_t *a, const uint16_t *bt, float *c, int m, int n, int k,
+                                int64_t lda, int64_t ldb, int64_t ldc, const oxgpu_epilogue *epilogue,
+                                unsigned flags, void *stream) {
+  return oxgpu::gemm_affine(0, a, bt, c, m, n, k, lda, ldb, ldc, epilogue, flags, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_tf32_affine(const float *a, const float *bt, float *c, int m, int n, int k, int64_t lda,
+                                int64_t ldb, int64_t ldc, const oxgpu_epilogue *epilogue, unsigned flags,
+                                void *stream) {
+  return oxgpu::gemm_affine(1, a, bt, c, m, n, k, lda, ldb, ldc, epilogue, flags, (cudaStream_t)stream);
 }
 
 int oxgpu_b200_shared_alloc(size_t bytes, void **ptr, unsigned char handle[64]) {

@@ -85,6 +85,13 @@ struct GemmParams {
   long long c_ld;
   int c_rows, c_cols;
   unsigned long long wait_budget_ns;
+  // Affine epilogue (AFFINE kernels only): C = alpha * (A B) + beta * C_in + bias,
+  // bias[N] broadcast over rows (null: none); C_in is read only when beta != 0 and
+  // may be C itself.
+  float alpha, beta;
+  const float *bias;
+  const float *c_in;
+  long long c_in_ld;
 };
 
 // Parameters of the fan-out kernels: the epilogue writes every staged 32x32
@@ -217,6 +224,42 @@ struct CrossSliceSum {
   }
 };
 
+// The affine epilogue on one 32-column chunk of one accumulator row (held by one
+// lane): v = (alpha * acc + beta * c_in) + bias, every step rounded on its own
+// (no fused multiply-add), so a host that applies the same three operations in
+// f32 to the plain GEMM's output gets the same bits.
+__device__ __forceinline__ void affine_chunk(uint32_t (&v)[32], const GemmParams &p, int row, int col) {
+  const bool use_c = p.beta != 0.0f && row < p.c_rows;
+  const float *c_row = use_c ? p.c_in + (long long)row * p.c_in_ld : nullptr;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const int cj = col + 4 * j;
+    float b[4] = {0.f, 0.f, 0.f, 0.f}, ci[4] = {0.f, 0.f, 0.f, 0.f};
+    if (cj + 4 <= p.c_cols) {
+      if (p.bias) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p.bias + cj));
+        b[0] = t.x, b[1] = t.y, b[2] = t.z, b[3] = t.w;
+      }
+      if (use_c) {
+        const float4 t = *reinterpret_cast<const float4 *>(c_row + cj);
+        ci[0] = t.x, ci[1] = t.y, ci[2] = t.z, ci[3] = t.w;
+      }
+    } else {
+      for (int q = 0; q < 4; q++)
+        if (cj + q < p.c_cols) {
+          if (p.bias) b[q] = __ldg(p.bias + cj + q);
+          if (use_c) ci[q] = c_row[cj + q];
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const float acc = __uint_as_float(v[4 * j + q]);
+      const float r = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, acc), __fmul_rn(p.beta, ci[q])), b[q]);
+      v[4 * j + q] = __float_as_uint(r);
+    }
+  }
+}
+
 // OUT16: C is stored as bf16 (round to nearest even) instead of f32 -- the
 // narrow-output epilogue the reference lists as future work
 // (docs/roadmap.md:67-71); the C map is then a bf16 map with 64-column boxes.
@@ -225,10 +268,13 @@ struct CrossSliceSum {
 // (the reference's 256-row B^T box): UMMA `ni` of a K step reads rows
 // [ni * BN/2, (ni + 1) * BN/2) of both CTAs' stages, so accumulator column j of
 // block ni is tile column (j / (BN/2)) * BN + ni * BN/2 + j % (BN/2).
-template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1>
+// AFFINE: the f32 epilogue applies alpha, beta * C_in and a bias row (affine_chunk).
+template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1,
+          bool AFFINE = false>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
 umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmParamsFanout, GemmParams>::type p) {
   static_assert(!(FANOUT && OUT16), "the fan-out epilogue writes f32");
+  static_assert(!(AFFINE && OUT16), "the affine epilogue writes f32");
   // A CTA owns BM_CTA rows of the tile as MI blocks of 128 rows (one UMMA each
   // per K step, all sharing the staged B^T rows).  Block `mi` of accumulator
   // set `set` is one hand-off unit between the issuer and the epilogue.
@@ -606,6 +652,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ptx::tmem_ld_wait();
           if (c + 1 < CHUNKS_PER_GROUP) ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
           else release_unit();
+          if constexpr (AFFINE) affine_chunk(cur, p, c_row + lane, chunk_col(c));
           // the previous store must be done reading the staging buffer
           if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();

@@ -13,7 +13,7 @@ import ctypes
 import torch
 
 from . import catalog
-from ._lib import check, lib
+from ._lib import EpilogueStruct, check, lib
 
 (VARIANT_AUTO, V_1CTA_128x256, V_1CTA_128x128, V_1CTA_256x128, V_2CTA_256x256, V_2CTA_256x128, V_SPLITK,
  V_2CTA_512x256, V_1CTA_256x256, V_CSPLITK_128x256, V_CSPLITK_128x128, V_2CTA_256x512) = range(12)
@@ -133,6 +133,31 @@ def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, 
     else:
         check(lib().oxgpu_b200_gemm_bf16(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k,
                                          a.stride(0), bt.stride(0), c.stride(0), flags, s))
+    return c
+
+
+def gemm_affine(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, alpha: float = 1.0,
+                beta: float = 0.0, bias: torch.Tensor | None = None, c_in: torch.Tensor | None = None,
+                flags: int = 0, stream=None) -> torch.Tensor:
+    """C = (alpha * (A B) + beta * C_in) + bias in the GEMM's epilogue (bf16 or
+    f32/TF32 operands by dtype).  c_in defaults to c (in-place) when beta != 0."""
+    kind = {torch.bfloat16: "bf16", torch.float32: "tf32"}.get(a.dtype)
+    if kind is None:
+        raise ValueError("operands must be bf16 or f32")
+    m, n, k = _check_operands(a, bt, a.dtype)
+    c = _out(c, m, n, a.device)
+    if beta != 0.0 and c_in is None:
+        c_in = c
+    if bias is not None and (bias.dtype != torch.float32 or tuple(bias.shape) != (n,) or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous f32 vector of length N")
+    if c_in is not None and (c_in.dtype != torch.float32 or tuple(c_in.shape) != (m, n) or c_in.stride(1) != 1):
+        raise ValueError("c_in must be f32 [M,N] with unit column stride")
+    ep = EpilogueStruct(alpha, beta, bias.data_ptr() if bias is not None else None,
+                        c_in.data_ptr() if c_in is not None else None,
+                        c_in.stride(0) if c_in is not None else 0)
+    fn = lib().oxgpu_b200_gemm_bf16_affine if kind == "bf16" else lib().oxgpu_b200_gemm_tf32_affine
+    check(fn(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0), bt.stride(0), c.stride(0),
+             ctypes.byref(ep), flags, ctypes.c_void_p(_stream(stream))))
     return c
 
 

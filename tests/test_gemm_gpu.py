@@ -618,6 +618,50 @@ def test_shared_buffer_is_a_tensor_view():
     buf.free()
 
 
+@pytest.mark.parametrize("variant", FANOUT_VARIANTS)
+@pytest.mark.parametrize("alpha,beta,use_bias", [(1.0, 0.0, True), (0.5, 2.0, True), (-1.25, 1.0, False),
+                                                 (2.0, 0.0, False)])
+def test_affine_epilogue(variant, alpha, beta, use_bias):
+    """C = (alpha * AB + beta * C_in) + bias in the GEMM's epilogue equals, bit for
+    bit, the same three f32 operations applied to the plain GEMM's output (which
+    the other tests hold against the oracle); ragged M and N."""
+    m, n, k = 300, 1284, 320
+    rng = np.random.default_rng(17)
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    a, bt = bf16_tensor(a_bits), bf16_tensor(bt_bits)
+    flags = gemm.make_flags(variant)
+    plain = gemm.gemm_bf16(a, bt, flags=flags)
+    check_bf16(a_bits, bt_bits, plain)
+    c_in = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(DEV)
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(DEV) if use_bias else None
+    expect = alpha * plain + beta * c_in
+    if use_bias:
+        expect = expect + bias
+    got = gemm.gemm_affine(a, bt, None, alpha, beta, bias, c_in, flags=flags)
+    assert torch.equal(got, expect)
+    # in place: C_in is C
+    c = c_in.clone()
+    gemm.gemm_affine(a, bt, c, alpha, beta, bias, flags=flags)
+    assert torch.equal(c, expect)
+
+
+def test_affine_epilogue_tf32_and_beta_zero_ignores_c_in():
+    m, n, k = 512, 768, 256
+    a = torch.empty(m, k, device=DEV)
+    bt = torch.empty(n, k, device=DEV)
+    gemm.fill_uniform(a, 1, 0)
+    gemm.fill_uniform(bt, 1, m * k)
+    plain = gemm.gemm_tf32(a, bt)
+    bias = torch.arange(n, device=DEV, dtype=torch.float32) * 0.25
+    poisoned = torch.full((m, n), float("nan"), device=DEV)
+    got = gemm.gemm_affine(a, bt, None, 3.0, 0.0, bias, poisoned)
+    assert torch.equal(got, 3.0 * plain + bias)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_affine(a, bt, None, 1.0, 0.0, flags=gemm.make_flags("1cta_256x128"))
+    with pytest.raises(OxgpuError):
+        gemm.gemm_affine(a, bt, None, 1.0, 0.0, torch.empty(n + 1, device=DEV)[1:])  # misaligned bias
+
+
 def test_launch_count_increases():
     before = gemm.launch_count()
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
