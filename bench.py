@@ -2,7 +2,7 @@
 """Benchmark of the dense GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload bf16_8192|tf32_4096|proj_a|proj_b|proj_c|cfg5] [--gather]
+                    [--workload bf16_8192|tf32_4096|tf32_8192|proj_a|proj_b|proj_c|cfg5] [--gather]
 
 One "step" is one GEMM over one set of synthetic operands.  Default workload:
 bf16 8192^3 (A row-major, B column-major = B^T[N,K] row-major, normal(0,1),
@@ -38,6 +38,7 @@ WORKLOADS = {
     # name: (kind, M, N, K, distribution, std, seed)
     "bf16_8192": ("bf16", 8192, 8192, 8192, "normal", 1.0, 2),
     "tf32_4096": ("tf32", 4096, 4096, 4096, "uniform", 1.0, 1),
+    "tf32_8192": ("tf32", 8192, 8192, 8192, "uniform", 1.0, 1),
     "proj_a": ("bf16", 8192, 28672, 8192, "normal", 0.02, 3),
     "proj_b": ("bf16", 8192, 8192, 28672, "normal", 0.02, 3),
     "proj_c": ("bf16", 128, 8192, 8192, "normal", 0.02, 3),
@@ -179,6 +180,7 @@ def run_reference(args):
 
 def metric_name(workload: str) -> str:
     return {"bf16_8192": "bf16 GEMM TFLOPS @8192^3", "tf32_4096": "TF32 GEMM TFLOPS @4096^3",
+            "tf32_8192": "TF32 GEMM TFLOPS @8192^3",
             "cfg5": "bf16 sharded GEMM TFLOPS M=32768 N=65536 K=8192"}.get(
                 workload, f"bf16 GEMM TFLOPS {workload}")
 
