@@ -962,9 +962,20 @@ int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_byte
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (k % 64 == 0 && n % 64 == 0 && k / 64 <= 65535 && aligned16(b) && aligned16(bt)) {
+    // whole 64 x 64 tiles: 16-byte accesses on both sides
+    dim3 grid64(n / 64, k / 64, 1);
+    if (element_bytes == 2)
+      transpose64_kernel<uint16_t><<<grid64, 256, 0, s>>>((const uint16_t *)b, (uint16_t *)bt, k, n);
+    else
+      transpose64_kernel<float><<<grid64, 256, 0, s>>>((const float *)b, (float *)bt, k, n);
+    OX_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return OXGPU_OK;
+  }
   dim3 grid((n + 31) / 32, (k + 31) / 32, 1), block(32, 8, 1);
   if (grid.y > 65535) return fail(OXGPU_E_TOO_LARGE, "K too large for the transpose grid");
-  cudaStream_t s = (cudaStream_t)stream;
   if (element_bytes == 2)
     transpose_kernel<uint16_t><<<grid, block, 0, s>>>((const uint16_t *)b, (uint16_t *)bt, k, n);
   else
@@ -980,9 +991,10 @@ int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
-  size_t blocks = (count + 255) / 256;
+  const int vec = aligned16(src) && aligned16(dst) ? 1 : 0;
+  size_t blocks = ((vec ? (count + 7) / 8 : count) + 255) / 256;
   if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
-  f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(src, dst, count);
+  f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(src, dst, count, vec);
   OX_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return OXGPU_OK;
@@ -1022,14 +1034,15 @@ static int fill(int dist, void *dst, size_t count, int element_bytes, uint32_t s
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
-  size_t blocks = (count + 255) / 256;
+  const int vec = aligned16(dst) ? 1 : 0;
+  size_t blocks = ((vec ? (count + 3) / 4 : count) + 255) / 256;
   if (blocks > (size_t)dev->sm_count * 16) blocks = (size_t)dev->sm_count * 16;
   cudaStream_t s = (cudaStream_t)stream;
   unsigned g = (unsigned)blocks;
-  if (dist == 0 && element_bytes == 4) synth_fill_kernel<0, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
-  else if (dist == 0) synth_fill_kernel<0, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
-  else if (element_bytes == 4) synth_fill_kernel<1, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
-  else synth_fill_kernel<1, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset);
+  if (dist == 0 && element_bytes == 4) synth_fill_kernel<0, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset, vec);
+  else if (dist == 0) synth_fill_kernel<0, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset, vec);
+  else if (element_bytes == 4) synth_fill_kernel<1, false><<<g, 256, 0, s>>>(dst, count, seed, scale, offset, vec);
+  else synth_fill_kernel<1, true><<<g, 256, 0, s>>>(dst, count, seed, scale, offset, vec);
   OX_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return OXGPU_OK;

@@ -110,6 +110,36 @@ __global__ void transpose_kernel(const T *__restrict__ src, T *__restrict__ dst,
   }
 }
 
+// Same re-layout for sizes that are multiples of 64 with 16-byte-aligned
+// pointers: 64 x 64 tiles, 16-byte global loads and stores on both sides (a
+// 2-byte element would otherwise move 64 bytes per warp access), the transposition
+// done through shared memory.  HBM-bound: 2 * rows * cols * sizeof(T) bytes.
+template <typename T>
+__global__ void __launch_bounds__(256) transpose64_kernel(const T *__restrict__ src, T *__restrict__ dst,
+                                                          int rows, int cols) {
+  constexpr int V = 16 / (int)sizeof(T);       // elements per 16-byte access
+  constexpr int VPR = 64 / V;                  // 16-byte accesses per tile row
+  constexpr int PITCH = sizeof(T) == 4 ? 65 : 66;
+  __shared__ T tile[64 * PITCH];
+  const int x0 = blockIdx.x * 64, y0 = blockIdx.y * 64;
+  for (int v = threadIdx.x; v < 64 * VPR; v += 256) {
+    const int r = v / VPR, cv = v % VPR;
+    const uint4 q = *reinterpret_cast<const uint4 *>(src + (int64_t)(y0 + r) * cols + x0 + cv * V);
+    const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+    for (int i = 0; i < V; i++) tile[r * PITCH + cv * V + i] = e[i];
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < 64 * VPR; v += 256) {
+    const int r = v / VPR, cv = v % VPR;       // row r of the transposed tile = column r of the source tile
+    uint4 q;
+    T *e = reinterpret_cast<T *>(&q);
+#pragma unroll
+    for (int i = 0; i < V; i++) e[i] = tile[(cv * V + i) * PITCH + r];
+    *reinterpret_cast<uint4 *>(dst + (int64_t)(x0 + r) * rows + y0 + cv * V) = q;
+  }
+}
+
 // ---- f32 -> bf16 bits, round to nearest even (run_gemm_h100.cu:26-30) ------------
 __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
   uint32_t u = __float_as_uint(f);
@@ -117,11 +147,25 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
   return (uint16_t)((u + 0x7fffu + lsb) >> 16);
 }
 
+// Eight elements per thread and step (two 16-byte loads, one 16-byte store) when
+// both pointers are 16-byte aligned, element by element otherwise and for the
+// tail.  HBM-bound: 6 bytes per element.
 __global__ void f32_to_bf16_kernel(const float *__restrict__ src, uint16_t *__restrict__ dst,
-                                   size_t count) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < count; i += stride) dst[i] = f32_to_bf16_bits(src[i]);
+                                   size_t count, int vector_ok) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t groups = vector_ok ? count / 8 : 0;
+  for (size_t g = tid; g < groups; g += stride) {
+    const float4 lo = reinterpret_cast<const float4 *>(src)[2 * g];
+    const float4 hi = reinterpret_cast<const float4 *>(src)[2 * g + 1];
+    uint4 out;
+    out.x = (uint32_t)f32_to_bf16_bits(lo.x) | ((uint32_t)f32_to_bf16_bits(lo.y) << 16);
+    out.y = (uint32_t)f32_to_bf16_bits(lo.z) | ((uint32_t)f32_to_bf16_bits(lo.w) << 16);
+    out.z = (uint32_t)f32_to_bf16_bits(hi.x) | ((uint32_t)f32_to_bf16_bits(hi.y) << 16);
+    out.w = (uint32_t)f32_to_bf16_bits(hi.z) | ((uint32_t)f32_to_bf16_bits(hi.w) << 16);
+    reinterpret_cast<uint4 *>(dst)[g] = out;
+  }
+  for (size_t i = groups * 8 + tid; i < count; i += stride) dst[i] = f32_to_bf16_bits(src[i]);
 }
 
 // ---- split-K reduction ----------------------------------------------------------
@@ -174,15 +218,31 @@ __device__ __forceinline__ float synth_normal(uint32_t seed, uint64_t index) {
   return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
 }
 
-// DIST 0 = uniform [-1,1), 1 = normal(0, scale).  OUT16: store bf16 bits.
+// DIST 0 = uniform [-1,1), 1 = normal(0, scale).  OUT16: store bf16 bits.  Each
+// thread produces four consecutive elements per step and stores them as one 16-
+// or 8-byte vector when `dst` is 16-byte aligned (vector_ok).
 template <int DIST, bool OUT16>
 __global__ void synth_fill_kernel(void *dst, size_t count, uint32_t seed, float scale,
-                                  uint64_t index_offset) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < count; i += stride) {
-    float v = DIST == 0 ? synth_uniform_pm1(seed, index_offset + i)
-                        : synth_normal(seed, index_offset + i) * scale;
+                                  uint64_t index_offset, int vector_ok) {
+  auto value = [&](size_t i) {
+    return DIST == 0 ? synth_uniform_pm1(seed, index_offset + i) : synth_normal(seed, index_offset + i) * scale;
+  };
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t groups = vector_ok ? count / 4 : 0;
+  for (size_t g = tid; g < groups; g += stride) {
+    const float v0 = value(4 * g), v1 = value(4 * g + 1), v2 = value(4 * g + 2), v3 = value(4 * g + 3);
+    if constexpr (OUT16) {
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(v0) | ((uint32_t)f32_to_bf16_bits(v1) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(v2) | ((uint32_t)f32_to_bf16_bits(v3) << 16);
+      reinterpret_cast<uint2 *>(dst)[g] = o;
+    } else {
+      reinterpret_cast<float4 *>(dst)[g] = make_float4(v0, v1, v2, v3);
+    }
+  }
+  for (size_t i = groups * 4 + tid; i < count; i += stride) {
+    const float v = value(i);
     if constexpr (OUT16) reinterpret_cast<uint16_t *>(dst)[i] = f32_to_bf16_bits(v);
     else reinterpret_cast<float *>(dst)[i] = v;
   }

@@ -395,6 +395,43 @@ def test_conversion_and_transpose_match_the_oracle(golden_dir):
     assert np.array_equal(got, b16.T)
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 64), (128, 192), (320, 256), (70, 45), (64, 100), (1, 9)])
+def test_transpose_tiled_and_edge_paths(rows, cols):
+    """Sizes that are multiples of 64 take the 16-byte-access kernel, the others
+    the element-wise one; both must be exact permutations, for 4- and 2-byte elements."""
+    rng = np.random.default_rng(rows * 7 + cols)
+    b = rng.standard_normal((rows, cols)).astype(np.float32)
+    assert np.array_equal(gemm.transpose(torch.from_numpy(b).to(DEV)).cpu().numpy(), b.T)
+    b16 = oracle.to_bf16(b)
+    got = gemm.transpose(bf16_tensor(b16)).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, b16.T)
+
+
+@pytest.mark.parametrize("count,skip", [(1, 0), (7, 0), (8, 0), (4099, 0), (4096, 1), (1000, 3)])
+def test_conversion_vector_and_tail_paths(count, skip):
+    """f32 -> bf16 with and without 16-byte alignment and with a ragged tail:
+    bit-equal to the oracle's round-to-nearest-even."""
+    rng = np.random.default_rng(count + skip)
+    x = (rng.standard_normal(count + skip) * 10.0 ** rng.integers(-20, 20, count + skip)).astype(np.float32)
+    xd = torch.from_numpy(x).to(DEV)[skip:]
+    got = gemm.f32_to_bf16(xd.contiguous() if skip == 0 else xd).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, oracle.to_bf16(x[skip:]))
+
+
+@pytest.mark.parametrize("count,skip", [(5, 0), (1 << 12, 0), ((1 << 12) + 3, 0), (1 << 12, 1)])
+def test_generators_are_index_functions(count, skip):
+    """The value of element i depends only on (seed, offset + i): the vector
+    path, the element path and an unaligned start all give the host generator's bits."""
+    buf = torch.empty(count + skip, device=DEV)
+    gemm.fill_uniform(buf[skip:], 9, 17)
+    assert np.array_equal(buf[skip:].cpu().numpy(), synth.uniform_pm1(9, count, offset=17))
+    whole = torch.empty(count + 4, device=DEV, dtype=torch.bfloat16)
+    part = torch.empty_like(whole)
+    gemm.fill_normal(whole, 4, 0.5, 0)
+    gemm.fill_normal(part[skip:], 4, 0.5, skip)
+    assert torch.equal(whole[skip:], part[skip:])
+
+
 def test_device_generators():
     u = torch.empty(1 << 16, device=DEV)
     gemm.fill_uniform(u, 5, 100)
