@@ -352,6 +352,12 @@ OXGPU_API int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int el
 /* f32 -> bf16 bits, round-to-nearest-even (run_gemm_h100.cu:26-30). */
 OXGPU_API int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *stream);
 
+/* Both steps in one pass: f32 B[K,N] -> bf16 B^T[N,K] (round to nearest even as
+ * above), for a caller holding a row-major f32 B (bench/bench.py:255-271 does the
+ * two steps with torch).  K and N multiples of 64, pointers 16-byte aligned. */
+OXGPU_API int oxgpu_b200_transpose_f32_to_bf16(const float *b, uint16_t *bt, int k, int n,
+                                               void *stream);
+
 /* Host-buffer entry point: A, B^T and C live in HOST memory (pinned or
  * pageable).  Uploads the operands, runs gemm_bf16 and downloads C, pipelined
  * over row blocks of A/C on internal streams; returns after C is complete on

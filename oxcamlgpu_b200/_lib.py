@@ -98,6 +98,7 @@ def lib() -> ctypes.CDLL:
                                    c_int, c_void_p], c_int),
         "oxgpu_b200_transpose": ([c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
         "oxgpu_b200_f32_to_bf16": ([c_void_p, c_void_p, sz, c_void_p], c_int),
+        "oxgpu_b200_transpose_f32_to_bf16": ([c_void_p, c_void_p, c_int, c_int, c_void_p], c_int),
         "oxgpu_b200_gemm_bf16_host": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                        ctypes.c_uint], c_int),
         "oxgpu_b200_gemm_tf32_host": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -985,6 +985,21 @@ int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_byte
   return OXGPU_OK;
 }
 
+int oxgpu_b200_transpose_f32_to_bf16(const float *b, uint16_t *bt, int k, int n, void *stream) {
+  if (!b || !bt) return fail(OXGPU_E_INVALID_ARG, "null pointer");
+  if (k <= 0 || n <= 0) return fail(OXGPU_E_INVALID_ARG, "K and N must be positive");
+  if (k % 64 || n % 64) return fail(OXGPU_E_SHAPE, "the fused re-layout takes K and N that are multiples of 64");
+  if (k / 64 > 65535) return fail(OXGPU_E_TOO_LARGE, "K too large for the transpose grid");
+  if (!aligned16(b) || !aligned16(bt)) return fail(OXGPU_E_ALIGN, "pointers must be 16-byte aligned");
+  int dev_index, st;
+  DeviceState *dev = nullptr;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  transpose64_f32_to_bf16_kernel<<<dim3(n / 64, k / 64, 1), 256, 0, (cudaStream_t)stream>>>(b, bt, k, n);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return OXGPU_OK;
+}
+
 int oxgpu_b200_f32_to_bf16(const float *src, uint16_t *dst, size_t count, void *stream) {
   if (!src || !dst) return fail(OXGPU_E_INVALID_ARG, "null pointer");
   if (count == 0) return OXGPU_OK;

@@ -147,6 +147,36 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
   return (uint16_t)((u + 0x7fffu + lsb) >> 16);
 }
 
+// B[K,N] f32 -> B^T[N,K] bf16 in one pass (the two steps a caller with a
+// row-major f32 B needs before the bf16 GEMM, bench/bench.py:255-271): the
+// rounding of f32_to_bf16_bits, the tiling of transpose64_kernel.  HBM-bound:
+// 6 bytes per element instead of 6 + 4 for the two kernels in a row.
+__global__ void __launch_bounds__(256) transpose64_f32_to_bf16_kernel(const float *__restrict__ src,
+                                                                      uint16_t *__restrict__ dst, int rows,
+                                                                      int cols) {
+  constexpr int PITCH = 66;
+  __shared__ uint16_t tile[64 * PITCH];
+  const int x0 = blockIdx.x * 64, y0 = blockIdx.y * 64;
+  for (int v = threadIdx.x; v < 64 * 16; v += 256) {  // 16 four-element loads per tile row
+    const int r = v >> 4, cv = v & 15;
+    const float4 q = *reinterpret_cast<const float4 *>(src + (int64_t)(y0 + r) * cols + x0 + cv * 4);
+    uint16_t *t = tile + r * PITCH + cv * 4;
+    t[0] = f32_to_bf16_bits(q.x);
+    t[1] = f32_to_bf16_bits(q.y);
+    t[2] = f32_to_bf16_bits(q.z);
+    t[3] = f32_to_bf16_bits(q.w);
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < 64 * 8; v += 256) {   // 8 eight-element stores per transposed row
+    const int r = v >> 3, cv = v & 7;
+    uint4 q;
+    uint16_t *e = reinterpret_cast<uint16_t *>(&q);
+#pragma unroll
+    for (int i = 0; i < 8; i++) e[i] = tile[(cv * 8 + i) * PITCH + r];
+    *reinterpret_cast<uint4 *>(dst + (int64_t)(x0 + r) * rows + y0 + cv * 8) = q;
+  }
+}
+
 // Eight elements per thread and step (two 16-byte loads, one 16-byte store) when
 // both pointers are 16-byte aligned, element by element otherwise and for the
 // tail.  HBM-bound: 6 bytes per element.

@@ -314,11 +314,24 @@ def f32_to_bf16(x: torch.Tensor, stream=None) -> torch.Tensor:
     return out
 
 
+def transpose_to_bf16(b: torch.Tensor, stream=None) -> torch.Tensor:
+    """f32 B[K,N] -> bf16 B^T[N,K] in one pass (K and N multiples of 64)."""
+    if not b.is_cuda or b.dim() != 2 or not b.is_contiguous() or b.dtype != torch.float32:
+        raise ValueError("expected a contiguous 2-D f32 CUDA tensor")
+    k, n = b.shape
+    bt = torch.empty(n, k, device=b.device, dtype=torch.bfloat16)
+    check(lib().oxgpu_b200_transpose_f32_to_bf16(b.data_ptr(), bt.data_ptr(), k, n,
+                                                 ctypes.c_void_p(_stream(stream))))
+    return bt
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor, element: str = "f32", flags: int = 0) -> torch.Tensor:
     """A[M,K] @ B[K,N] the way the reference's bench drives its kernel
     (bench.py:255-271): convert to the input width, re-lay B K-major, launch."""
     if element == "bf16":
         a16 = a if a.dtype == torch.bfloat16 else f32_to_bf16(a.contiguous())
+        if b.dtype == torch.float32 and b.shape[0] % 64 == 0 and b.shape[1] % 64 == 0:
+            return gemm_bf16(a16, transpose_to_bf16(b.contiguous()), flags=flags)
         b16 = b if b.dtype == torch.bfloat16 else f32_to_bf16(b.contiguous())
         return gemm_bf16(a16, transpose(b16.contiguous()), flags=flags)
     return gemm_tf32(a.contiguous(), transpose(b.contiguous()), flags=flags)

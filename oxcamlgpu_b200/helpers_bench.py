@@ -64,6 +64,8 @@ def main() -> None:
 
     report("transpose f32", 2 * n * n * 4, _median_ms(lambda: gemm.transpose(f32), slab, args.repeat))
     report("transpose bf16", 2 * n * n * 2, _median_ms(lambda: gemm.transpose(b16), slab, args.repeat))
+    report("transpose + f32 -> bf16, one pass", n * n * 6,
+           _median_ms(lambda: gemm.transpose_to_bf16(f32), slab, args.repeat))
     report("f32 -> bf16", n * n * 6, _median_ms(lambda: gemm.f32_to_bf16(f32), slab, args.repeat))
     report("fill uniform f32", n * n * 4, _median_ms(lambda: gemm.fill_uniform(f32, 1, 0), slab, args.repeat))
     report("fill normal bf16", n * n * 2, _median_ms(lambda: gemm.fill_normal(b16, 2, 1.0, 0), slab, args.repeat))

@@ -407,6 +407,16 @@ def test_transpose_tiled_and_edge_paths(rows, cols):
     assert np.array_equal(got, b16.T)
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 64), (128, 320), (448, 192)])
+def test_fused_relayout_and_conversion(rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    b = (rng.standard_normal((rows, cols)) * 10.0 ** rng.integers(-10, 10, (rows, cols))).astype(np.float32)
+    got = gemm.transpose_to_bf16(torch.from_numpy(b).to(DEV)).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, oracle.to_bf16(b).T)
+    with pytest.raises(OxgpuError):
+        gemm.transpose_to_bf16(torch.zeros(70, 64, device=DEV))
+
+
 @pytest.mark.parametrize("count,skip", [(1, 0), (7, 0), (8, 0), (4099, 0), (4096, 1), (1000, 3)])
 def test_conversion_vector_and_tail_paths(count, skip):
     """f32 -> bf16 with and without 16-byte alignment and with a ragged tail:
