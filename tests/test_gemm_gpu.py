@@ -709,6 +709,46 @@ def test_affine_epilogue_tf32_and_beta_zero_ignores_c_in():
         gemm.gemm_affine(a, bt, None, 1.0, 0.0, torch.empty(n + 1, device=DEV)[1:])  # misaligned bias
 
 
+def test_concurrent_host_threads_on_their_own_streams():
+    """The entry points are reentrant per stream: two host threads launch
+    different problems on their own streams at the same time; every result must
+    equal the one computed alone."""
+    import threading
+    shapes = [(640, 768, 512), (300, 520, 200)]
+    data, alone = [], []
+    for i, (m, n, k) in enumerate(shapes):
+        a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+        gemm.fill_normal(a, 30 + i, 1.0, 0)
+        gemm.fill_normal(bt, 30 + i, 1.0, m * k)
+        data.append((a, bt))
+        alone.append(gemm.gemm_bf16(a, bt))
+    torch.cuda.synchronize()
+    failures = []
+
+    def worker(i):
+        try:
+            stream = torch.cuda.Stream()
+            a, bt = data[i]
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    c = gemm.gemm_bf16(a, bt)
+                    bias = torch.zeros(bt.shape[0], device=DEV)
+                    c2 = gemm.gemm_affine(a, bt, None, 1.0, 0.0, bias)
+                stream.synchronize()
+            if not (torch.equal(c, alone[i]) and torch.equal(c2, alone[i])):
+                failures.append(i)
+        except Exception as e:  # noqa: BLE001
+            failures.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures
+
+
 def test_launch_count_increases():
     before = gemm.launch_count()
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
