@@ -32,7 +32,7 @@ __device__ __forceinline__ float simt_load(const void *base, int64_t index) {
 }
 
 template <int IN_MODE>
-__global__ void __launch_bounds__(kSimtThreads)
+__global__ void __launch_bounds__(kSimtThreads, 2)
 simt_gemm_exact_kernel(const void *__restrict__ a, const void *__restrict__ bt, float *__restrict__ c,
                        int m, int n, int k, int64_t lda, int64_t ldb, int64_t ldc) {
   // K-slices stored k-major ([kk][row]) so the inner product reads are
