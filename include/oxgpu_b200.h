@@ -237,6 +237,22 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
                                       unsigned flags, void *workspace, size_t workspace_bytes,
                                       void *stream);
 
+/* f32 operands at close to f32 accuracy on the tensor cores ("3xTF32"): each
+ * operand is split into its TF32 part and the exact remainder, and one TF32
+ * GEMM over 3K accumulates hi*hi + hi*lo + lo*hi in f32 (the dropped lo*lo term
+ * is 2^-20 relative).  For f32-in callers who need the host check's bound
+ * 1e-5 * sqrt(K) * max|A| * max|B| against UNROUNDED inputs
+ * (test/hardware/run_gemm_h100.cu:150-162 runs on the inputs as given) at more
+ * than the exact kernel's CUDA-core rate; plain TF32 misses that bound by a
+ * factor of about 20.  K % 4 == 0.  workspace: oxgpu_b200_f32_split_workspace_bytes
+ * (m, n, k) = 12 * K * (M + N) bytes, 16-byte aligned, for the split operands.
+ * flags as for oxgpu_b200_gemm_tf32 (applied to the M x N x 3K problem). */
+OXGPU_API size_t oxgpu_b200_f32_split_workspace_bytes(int m, int n, int k);
+OXGPU_API int oxgpu_b200_gemm_f32_split(const float *a, const float *bt, float *c, int m, int n,
+                                        int k, int64_t lda, int64_t ldb, int64_t ldc,
+                                        unsigned flags, void *workspace, size_t workspace_bytes,
+                                        void *stream);
+
 /* GEMM with an affine epilogue: C = alpha * (A B) + beta * C_in + bias, applied to
  * the accumulator on its way from TMEM to the store (the fused epilogue beyond
  * the reference's plain overwrite, examples/kernels/gemm.ml:143-161; its

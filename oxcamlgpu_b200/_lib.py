@@ -84,6 +84,9 @@ def lib() -> ctypes.CDLL:
                                          c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_gemm_tf32_fanout": ([c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int, c_int,
                                          c_int, i64, i64, i64, ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_f32_split_workspace_bytes": ([c_int, c_int, c_int], sz),
+        "oxgpu_b200_gemm_f32_split": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
+                                       ctypes.c_uint, c_void_p, sz, c_void_p], c_int),
         "oxgpu_b200_gemm_bf16_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                          ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_gemm_tf32_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,

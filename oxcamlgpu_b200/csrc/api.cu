@@ -823,6 +823,40 @@ int oxgpu_b200_gemm_tf32_fanout(const float *a, const float *bt, float *const *c
   return oxgpu::gemm_fanout(1, a, bt, c_dests, n_dests, m, n, k, lda, ldb, ldc, flags, (cudaStream_t)stream);
 }
 
+size_t oxgpu_b200_f32_split_workspace_bytes(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return 3 * (size_t)k * ((size_t)m + (size_t)n) * sizeof(float);
+}
+
+int oxgpu_b200_gemm_f32_split(const float *a, const float *bt, float *c, int m, int n, int k, int64_t lda,
+                              int64_t ldb, int64_t ldc, unsigned flags, void *workspace,
+                              size_t workspace_bytes, void *stream) {
+  using namespace oxgpu;
+  int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, 4);
+  if (st) return st;
+  if ((long long)k * 3 > 0x7fffffffLL) return fail(OXGPU_E_TOO_LARGE, "K too large for the three-piece split");
+  const size_t need = oxgpu_b200_f32_split_workspace_bytes(m, n, k);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(OXGPU_E_INVALID_ARG, "split workspace missing, misaligned or too small");
+  int dev_index;
+  DeviceState *dev = nullptr;
+  if ((st = current_device(&dev_index, &dev))) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  float *a3 = (float *)workspace;
+  float *b3 = a3 + 3 * (size_t)k * m;
+  auto blocks_for = [&](int rows) {
+    size_t b = ((size_t)rows * (k / 4) + 255) / 256;
+    const size_t most = (size_t)dev->sm_count * 16;
+    return (unsigned)(b > most ? most : (b ? b : 1));
+  };
+  split_tf32_kernel<<<blocks_for(m), 256, 0, s>>>(a, a3, m, k, lda, 0);
+  OX_CUDA(cudaGetLastError());
+  split_tf32_kernel<<<blocks_for(n), 256, 0, s>>>(bt, b3, n, k, ldb, 1);
+  OX_CUDA(cudaGetLastError());
+  g_launches.fetch_add(2, std::memory_order_relaxed);
+  return gemm_buffers(1, a3, b3, c, m, n, 3 * k, 3 * (int64_t)k, 3 * (int64_t)k, ldc, flags, nullptr, 0, s);
+}
+
 int oxgpu_b200_gemm_bf16_affine(const uint16_t *a, const uint16_t *bt, float *c, int m, int n, int k,
                                 int64_t lda, int64_t ldb, int64_t ldc, const oxgpu_epilogue *epilogue,
                                 unsigned flags, void *stream) {

@@ -198,6 +198,38 @@ __global__ void f32_to_bf16_kernel(const float *__restrict__ src, uint16_t *__re
   for (size_t i = groups * 8 + tid; i < count; i += stride) dst[i] = f32_to_bf16_bits(src[i]);
 }
 
+// ---- f32 operands split into TF32 pieces ------------------------------------------
+// x = hi + lo with hi = x truncated to TF32 (what the matrix unit would keep,
+// run_gemm_h100.cu:40-44) and lo = x - hi (exact in f32; the unit truncates it
+// again).  Row r of dst holds three K-long pieces: [hi | hi | lo] (order 0, for A)
+// or [hi | lo | hi] (order 1, for B^T), so that one TF32 GEMM over 3K computes
+// hi*hi + hi*lo + lo*hi -- the f32 product up to a 2^-20 relative term -- with f32
+// accumulation.  k % 4 == 0, 16-byte aligned rows.
+__global__ void split_tf32_kernel(const float *__restrict__ src, float *__restrict__ dst, int rows, int k,
+                                  int64_t ld_src, int order) {
+  const int k4 = k >> 2;
+  const size_t total = (size_t)rows * k4;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int r = (int)(i / k4), q = (int)(i - (size_t)r * k4);
+    const float4 x = *reinterpret_cast<const float4 *>(src + (int64_t)r * ld_src + 4 * q);
+    float4 hi, lo;
+    hi.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
+    hi.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+    hi.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
+    hi.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
+    lo.x = __fsub_rn(x.x, hi.x);
+    lo.y = __fsub_rn(x.y, hi.y);
+    lo.z = __fsub_rn(x.z, hi.z);
+    lo.w = __fsub_rn(x.w, hi.w);
+    float *row = dst + (size_t)r * 3 * k + 4 * q;
+    *reinterpret_cast<float4 *>(row) = hi;
+    *reinterpret_cast<float4 *>(row + k) = order == 0 ? hi : lo;
+    *reinterpret_cast<float4 *>(row + 2 * k) = order == 0 ? lo : hi;
+  }
+}
+
 // ---- split-K reduction ----------------------------------------------------------
 // C[r, :] = sum over slices s (ascending, so the result is deterministic) of
 // workspace[s * slice_rows + r, :].  n4 = N / 4 (rows are float4 aligned).

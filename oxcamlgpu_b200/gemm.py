@@ -136,6 +136,23 @@ def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, 
     return c
 
 
+def gemm_f32_split(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, flags: int = 0,
+                   workspace: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """f32 A[M,K], B^T[N,K] -> f32 C at close to f32 accuracy on the tensor cores:
+    operands split into TF32 part + remainder, one TF32 GEMM over 3K."""
+    m, n, k = _check_operands(a, bt, torch.float32)
+    c = _out(c, m, n, a.device)
+    need = lib().oxgpu_b200_f32_split_workspace_bytes(m, n, k)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    check(lib().oxgpu_b200_gemm_f32_split(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0),
+                                          bt.stride(0), c.stride(0), flags, workspace.data_ptr(),
+                                          workspace.numel() * workspace.element_size(),
+                                          ctypes.c_void_p(_stream(stream))))
+    c._oxgpu_keepalive = workspace
+    return c
+
+
 def gemm_affine(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None, alpha: float = 1.0,
                 beta: float = 0.0, bias: torch.Tensor | None = None, c_in: torch.Tensor | None = None,
                 flags: int = 0, stream=None) -> torch.Tensor:

@@ -76,6 +76,13 @@ def main() -> None:
     ms = _median_ms(lambda: gemm.gemm_exact(a, a, gemm.INPUT_NONE), slab, max(3, args.repeat // 3))
     print(f"{'exact f32 GEMM ' + str(m) + '^3':34s} {ms:8.4f} ms {2.0 * m ** 3 / ms * 1e-9:8.2f} TFLOP/s "
           "(2 rounded operations per MAC on the CUDA cores)", flush=True)
+    # the same f32 problem on the tensor cores at close to f32 accuracy (three TF32 pieces over 3K)
+    m2 = min(n, 4096)
+    a2 = f32[:m2, :m2].contiguous()
+    ws = torch.empty(gemm.lib().oxgpu_b200_f32_split_workspace_bytes(m2, m2, m2), dtype=torch.uint8, device=dev)
+    ms = _median_ms(lambda: gemm.gemm_f32_split(a2, a2, workspace=ws), slab, max(3, args.repeat // 2))
+    print(f"{'f32 split GEMM ' + str(m2) + '^3':34s} {ms:8.4f} ms {2.0 * m2 ** 3 / ms * 1e-9:8.2f} TFLOP/s "
+          "of f32-equivalent work (split kernels + one TF32 GEMM over 3K)", flush=True)
     gemm.device_status()
 
 

@@ -749,6 +749,35 @@ def test_concurrent_host_threads_on_their_own_streams():
     assert not failures, failures
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (300, 520, 200), (1024, 768, 1024), (128, 264, 2048)])
+def test_f32_split_meets_the_strict_bound_on_unrounded_inputs(m, n, k):
+    """f32 operands as given (no TF32 rounding on the oracle's side): the
+    three-piece TF32 split stays inside 1e-5 * sqrt(K) * max|A| * max|B|, the
+    bound stated for f32-in cases, where the plain TF32 path misses it."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    bt = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+    expect = oracle.gemm_kmajor(a, bt, oracle.MODE_NONE, threads=oracle.max_threads())
+    ta, tb = torch.from_numpy(a).to(DEV), torch.from_numpy(bt).to(DEV)
+    tol = strict_tol(k, float(np.abs(a).max()), float(np.abs(bt).max()))
+    got = gemm.gemm_f32_split(ta, tb).cpu().numpy()
+    err = float(np.abs(got - expect).max())
+    assert err <= tol, (err, tol)
+    plain = gemm.gemm_tf32(ta, tb).cpu().numpy()
+    assert float(np.abs(plain - expect).max()) > tol          # why the split exists
+    exact = gemm.gemm_exact(ta, tb, gemm.INPUT_NONE).cpu().numpy()
+    assert np.array_equal(exact.view(np.uint32), expect.view(np.uint32))
+    print(f"split err {err:.3e} plain TF32 err {float(np.abs(plain - expect).max()):.3e} tol {tol:.3e}")
+
+
+def test_f32_split_contract():
+    a = torch.zeros(128, 64, device=DEV)
+    with pytest.raises(OxgpuError):
+        gemm.gemm_f32_split(a, a, workspace=torch.empty(16, dtype=torch.uint8, device=DEV))
+    with pytest.raises(OxgpuError):
+        gemm.gemm_f32_split(torch.zeros(128, 66, device=DEV)[:, :62], torch.zeros(128, 66, device=DEV)[:, :62])
+
+
 def test_launch_count_increases():
     before = gemm.launch_count()
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
