@@ -64,6 +64,25 @@ def blocks_to_row_major(gathered: torch.Tensor) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(m, world * w).contiguous()
 
 
+def peers_alive(group=None, timeout_s: float = 5.0) -> bool:
+    """Host-side liveness check before a launch that writes into other ranks'
+    memory: True if every rank of the group reached this call within the
+    time-out.  A rank that has left (between steps, nothing in flight) shows up
+    here as False on the others instead of as stores into memory nobody owns.
+    Uses the process group only; no GPU work."""
+    import datetime
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return True
+    try:
+        if dist.get_backend(group) == "gloo":
+            dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=timeout_s))
+        else:
+            dist.barrier(group=group)       # bounded by the group's own time-out
+        return True
+    except Exception:                        # noqa: BLE001 - any transport or time-out error means "not all here"
+        return False
+
+
 class ColumnShardedGemm:
     """bf16 GEMM with B and C column-sharded across the ranks of a process
     group and A replicated.  Each rank launches the single-GPU kernel on its
@@ -134,9 +153,14 @@ class FusedGatherGemm:
                 self._opened.append(ptr)
                 self._dest_base.append(ptr)
 
-    def run(self, a: torch.Tensor, bt_shard: torch.Tensor) -> None:
+    def run(self, a: torch.Tensor, bt_shard: torch.Tensor, check_peers_s: float | None = None) -> None:
+        """Launch this rank's GEMM.  With check_peers_s, first make sure on the
+        host that every rank is still there (peers_alive) and raise RuntimeError
+        without launching if not."""
         if tuple(bt_shard.shape) != (self.width, self.k) or tuple(a.shape) != (self.m, self.k):
             raise ValueError("operand shapes do not match this rank's shard")
+        if check_peers_s is not None and not peers_alive(self.group, check_peers_s):
+            raise RuntimeError("a rank of the group did not answer: nothing was launched")
         if self.width == 0:
             return
         dests = [base + self.n0 * 4 for base in self._dest_base]
@@ -148,12 +172,13 @@ class FusedGatherGemm:
             dist.barrier(group=self.group)
         return self.c
 
-    def close(self) -> None:
-        """Unmap the peers' buffers, then (after a barrier) free this rank's."""
+    def close(self, barrier: bool = True) -> None:
+        """Unmap the peers' buffers, then (after a barrier, unless a rank is
+        known to be gone) free this rank's."""
         for ptr in self._opened:
             self._gemm.shared_close(ptr)
         self._opened = []
-        if self.world > 1:
+        if self.world > 1 and barrier:
             dist.barrier(group=self.group)
         self.c = None
         self._buf.free()

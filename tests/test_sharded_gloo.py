@@ -141,3 +141,37 @@ def test_rank_failure_surfaces_as_an_error_not_a_hang():
         got[r] = msg
     assert got.get(1) == "failed before the gather" and procs[1].exitcode == 3
     assert got.get(0, "").startswith("error: ") and procs[0].exitcode == 0
+
+
+def _liveness_worker(rank, world, port, results):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    first = sharded.peers_alive(timeout_s=5.0)          # everybody is here
+    if rank == 1:
+        results.put((rank, first, None))
+        results.close()
+        results.join_thread()
+        os._exit(0)                                     # leaves between steps
+    second = sharded.peers_alive(timeout_s=2.0)         # rank 1 is gone
+    results.put((rank, first, second))
+    results.close()
+    results.join_thread()
+    os._exit(0)
+
+
+def test_peers_alive_reports_a_departed_rank():
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_liveness_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert all(not p.is_alive() for p in procs), "a rank hung"
+    got = {}
+    while not results.empty():
+        r, first, second = results.get()
+        got[r] = (first, second)
+    assert got[1][0] is True and got[0] == (True, False), got
