@@ -101,7 +101,7 @@ def _departing_worker(rank, world, port, results):
         fused = sharded.FusedGatherGemm(m, n, k)
         shard = sharded.shard_rows_of_bt(bt, rank, world)
         fused.run(a, shard, check_peers_s=10.0)
-        c = fused.finish()
+        c = fused.finish().clone()           # the shared buffer is freed by close()
         step1_ok = bool(torch.equal(c, gemm.gemm_bf16(a, bt)))
         if rank == 1:
             fused.close(barrier=False)
