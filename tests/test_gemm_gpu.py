@@ -513,6 +513,9 @@ def test_tf32_4096_cubed():
     assert float((c - exact).abs().max()) <= tol
     c2 = gemm.gemm_tf32(a * 2, bt)
     assert torch.equal(c2, c * 2)
+    # the reference's own entry point with the reference's own maps (the drop-in call)
+    via_entry = gemm.run_catalog_entry("gemm_fast", a, bt)
+    assert float((via_entry - exact).abs().max()) <= tol and torch.equal(via_entry, c)
 
 
 def test_bf16_8192_cubed():
@@ -533,9 +536,12 @@ def test_bf16_8192_cubed():
     exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
     assert np.array_equal(exact[rows].cpu().numpy(), expect)
     assert float((c - exact).abs().max()) <= tol
-    for variant in ("1cta_128x256", "2cta_256x256", "2cta_256x128"):
+    for variant in ("1cta_128x256", "2cta_256x256", "2cta_256x128", "2cta_256x512"):
         cv = gemm.gemm_bf16(a, bt, flags=gemm.make_flags(variant))
         assert float((cv - exact).abs().max()) <= tol
+    # the reference's own entry point with the reference's own maps (the drop-in call)
+    via_entry = gemm.run_catalog_entry("gemm_bf16_fast", a, bt)
+    assert float((via_entry - exact).abs().max()) <= tol and torch.equal(via_entry, c)
 
 
 @pytest.mark.parametrize("m,n,k", [(8192, 28672, 8192), (8192, 8192, 28672), (128, 8192, 8192)])
