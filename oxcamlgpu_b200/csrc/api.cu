@@ -997,11 +997,12 @@ int oxgpu_b200_transpose(const void *b, void *bt, int k, int n, int element_byte
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   cudaStream_t s = (cudaStream_t)stream;
-  if (k % 64 == 0 && n % 64 == 0 && k / 64 <= 65535 && aligned16(b) && aligned16(bt)) {
-    // whole 64 x 64 tiles: 16-byte accesses on both sides
-    dim3 grid64(n / 64, k / 64, 1);
+  const int tile_cols = 256 / element_bytes;
+  if (k % 64 == 0 && n % tile_cols == 0 && k / 64 <= 65535 && aligned16(b) && aligned16(bt)) {
+    // whole tiles of 64 rows x 256 bytes: 16-byte accesses on both sides
+    dim3 grid64(n / tile_cols, k / 64, 1);
     if (element_bytes == 2)
-      transpose64_kernel<uint16_t><<<grid64, 256, 0, s>>>((const uint16_t *)b, (uint16_t *)bt, k, n);
+      transpose64_pairs_kernel<<<grid64, 256, 0, s>>>((const uint16_t *)b, (uint16_t *)bt, k, n);
     else
       transpose64_kernel<float><<<grid64, 256, 0, s>>>((const float *)b, (float *)bt, k, n);
     OX_CUDA(cudaGetLastError());

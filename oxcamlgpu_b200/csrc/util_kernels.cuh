@@ -110,18 +110,24 @@ __global__ void transpose_kernel(const T *__restrict__ src, T *__restrict__ dst,
   }
 }
 
-// Same re-layout for sizes that are multiples of 64 with 16-byte-aligned
-// pointers: 64 x 64 tiles, 16-byte global loads and stores on both sides (a
-// 2-byte element would otherwise move 64 bytes per warp access), the transposition
-// done through shared memory.  HBM-bound: 2 * rows * cols * sizeof(T) bytes.
+// Same re-layout with 16-byte global accesses on both sides, for 16-byte-aligned
+// pointers, rows % 64 == 0 and cols % kTransposeCols<T> == 0: tiles of 64 rows x
+// 256 bytes (64 f32 or 128 bf16 columns, so every thread has four 16-byte loads
+// in flight), transposed through shared memory.  HBM-bound:
+// 2 * rows * cols * sizeof(T) bytes.
+template <typename T>
+constexpr int kTransposeCols = 256 / (int)sizeof(T);
+
 template <typename T>
 __global__ void __launch_bounds__(256) transpose64_kernel(const T *__restrict__ src, T *__restrict__ dst,
                                                           int rows, int cols) {
   constexpr int V = 16 / (int)sizeof(T);       // elements per 16-byte access
-  constexpr int VPR = 64 / V;                  // 16-byte accesses per tile row
-  constexpr int PITCH = sizeof(T) == 4 ? 65 : 66;
+  constexpr int TC = kTransposeCols<T>;        // tile columns
+  constexpr int VPR = TC / V;                  // 16-byte accesses per source tile row (16)
+  constexpr int VPO = 64 / V;                  // 16-byte accesses per transposed tile row
+  constexpr int PITCH = TC + (sizeof(T) == 4 ? 1 : 2);
   __shared__ T tile[64 * PITCH];
-  const int x0 = blockIdx.x * 64, y0 = blockIdx.y * 64;
+  const int x0 = blockIdx.x * TC, y0 = blockIdx.y * 64;
   for (int v = threadIdx.x; v < 64 * VPR; v += 256) {
     const int r = v / VPR, cv = v % VPR;
     const uint4 q = *reinterpret_cast<const uint4 *>(src + (int64_t)(y0 + r) * cols + x0 + cv * V);
@@ -130,13 +136,45 @@ __global__ void __launch_bounds__(256) transpose64_kernel(const T *__restrict__ 
     for (int i = 0; i < V; i++) tile[r * PITCH + cv * V + i] = e[i];
   }
   __syncthreads();
-  for (int v = threadIdx.x; v < 64 * VPR; v += 256) {
-    const int r = v / VPR, cv = v % VPR;       // row r of the transposed tile = column r of the source tile
+  for (int v = threadIdx.x; v < TC * VPO; v += 256) {
+    const int r = v / VPO, cv = v % VPO;       // row r of the transposed tile = column r of the source tile
     uint4 q;
     T *e = reinterpret_cast<T *>(&q);
 #pragma unroll
     for (int i = 0; i < V; i++) e[i] = tile[(cv * V + i) * PITCH + r];
     *reinterpret_cast<uint4 *>(dst + (int64_t)(x0 + r) * rows + y0 + cv * V) = q;
+  }
+}
+
+// The 2-byte case of the above with half the shared-memory instructions: the
+// tile is kept as 32-bit pairs of neighbouring columns, and a thread of the
+// store phase reads eight pairs (eight source rows, two source columns) and
+// writes 16 bytes of each of the two transposed rows.
+__global__ void __launch_bounds__(256) transpose64_pairs_kernel(const uint16_t *__restrict__ src,
+                                                                uint16_t *__restrict__ dst, int rows, int cols) {
+  constexpr int PITCH = 65;                     // 64 pairs per tile row + 1
+  __shared__ uint32_t tile[64 * PITCH];
+  const int x0 = blockIdx.x * 128, y0 = blockIdx.y * 64;
+  for (int v = threadIdx.x; v < 64 * 16; v += 256) {
+    const int r = v >> 4, cv = v & 15;
+    const uint4 q = *reinterpret_cast<const uint4 *>(src + (int64_t)(y0 + r) * cols + x0 + cv * 8);
+    uint32_t *t = tile + r * PITCH + cv * 4;
+    t[0] = q.x, t[1] = q.y, t[2] = q.z, t[3] = q.w;
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < 64 * 8; v += 256) {
+    const int pair = v >> 3, cv = v & 7;        // source columns 2*pair, 2*pair+1; source rows 8*cv .. 8*cv+7
+    uint32_t w[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) w[e] = tile[(cv * 8 + e) * PITCH + pair];
+    uint4 even, odd;                            // transposed rows 2*pair and 2*pair+1
+    even.x = __byte_perm(w[0], w[1], 0x5410), odd.x = __byte_perm(w[0], w[1], 0x7632);
+    even.y = __byte_perm(w[2], w[3], 0x5410), odd.y = __byte_perm(w[2], w[3], 0x7632);
+    even.z = __byte_perm(w[4], w[5], 0x5410), odd.z = __byte_perm(w[4], w[5], 0x7632);
+    even.w = __byte_perm(w[6], w[7], 0x5410), odd.w = __byte_perm(w[6], w[7], 0x7632);
+    uint16_t *o = dst + (int64_t)(x0 + 2 * pair) * rows + y0 + cv * 8;
+    *reinterpret_cast<uint4 *>(o) = even;
+    *reinterpret_cast<uint4 *>(o + rows) = odd;
   }
 }
 

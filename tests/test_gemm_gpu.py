@@ -395,10 +395,11 @@ def test_conversion_and_transpose_match_the_oracle(golden_dir):
     assert np.array_equal(got, b16.T)
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 64), (128, 192), (320, 256), (70, 45), (64, 100), (1, 9)])
+@pytest.mark.parametrize("rows,cols", [(64, 64), (128, 192), (320, 256), (64, 128), (192, 384), (70, 45), (64, 100), (1, 9)])
 def test_transpose_tiled_and_edge_paths(rows, cols):
-    """Sizes that are multiples of 64 take the 16-byte-access kernel, the others
-    the element-wise one; both must be exact permutations, for 4- and 2-byte elements."""
+    """Whole tiles (64 rows x 256 bytes) take the 16-byte-access kernel, other
+    sizes the element-wise one; both must be exact permutations, for 4- and
+    2-byte elements."""
     rng = np.random.default_rng(rows * 7 + cols)
     b = rng.standard_normal((rows, cols)).astype(np.float32)
     assert np.array_equal(gemm.transpose(torch.from_numpy(b).to(DEV)).cpu().numpy(), b.T)
