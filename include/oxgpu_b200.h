@@ -239,7 +239,7 @@ OXGPU_API int oxgpu_b200_gemm_bf16_ws(const uint16_t *a, const uint16_t *bt, flo
 
 /* f32 operands at close to f32 accuracy on the tensor cores ("3xTF32"): each
  * operand is split into its TF32 part and the exact remainder, and one TF32
- * GEMM over 3K accumulates hi*hi + hi*lo + lo*hi in f32 (the dropped lo*lo term
+ * GEMM over 3K accumulates hi*lo + lo*hi + hi*hi in f32 (the dropped lo*lo term
  * is 2^-20 relative).  For f32-in callers who need the host check's bound
  * 1e-5 * sqrt(K) * max|A| * max|B| against UNROUNDED inputs
  * (test/hardware/run_gemm_h100.cu:150-162 runs on the inputs as given) at more

@@ -351,17 +351,24 @@ int choose_variant(const DeviceState &dev, int m, int n, int k) {
   // 256x256 (48 instead of 64 bytes per clock per SM at full tensor rate), which
   // is what limits the kernel at boost clocks: 95 % against 91.5 % of cuBLAS at
   // bf16 8192^3, even though it cannot double-buffer its accumulator.
-  if (tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
-  if (tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
-  if (tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
+  // (A tile taller than the problem is mostly padding: with M = 128 a 512-row
+  // pair tile would do four times the work, 174 us instead of 111 us at
+  // 128 x 28672 x 8192.  Tall tiles need M to fill at least three quarters of them.)
+  auto fills = [&](int tm) { return 4LL * m >= 3LL * (long long)((m + tm - 1) / tm) * tm; };
+  if (fills(512) && tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
+  if (fills(256) && tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
+  if (fills(256) && tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
   // Fewer tiles than SMs: these problems stream one operand from HBM and the
   // time is set by the busiest SM's bytes.  A full wave of one-CTA tiles first
   // (128-column tiles stream B^T faster than 256-column ones when M is a single
-  // tile row: 111 us against 173 us at 128 x 28672 x 8192) ...
+  // tile row) ...
   if (tiles(128, 256) >= dev.sm_count) return VARIANT_1CTA_128x256;
   if (tiles(128, 128) >= dev.sm_count) return VARIANT_1CTA_128x128;
   // ... otherwise, when K is long, split it across a cluster so every SM has work.
-  if (k >= 2048 && tiles(128, 256) * 2 <= dev.sm_count && n % 256 == 0) return VARIANT_CLUSTER_SPLITK_128x256;
+  // 128-column tiles with few, long slices: the reduction at the end costs
+  // microseconds, so a slice should be at least 32 K blocks (128 x 4096 x 4096:
+  // 22.6 us with 2 slices of 32 against 32.8 us with 8 slices of 8; 128 x 8192 x
+  // 8192: 41.0 us with 128-column tiles x 2 against 43.0 us with 256 x 4).
   if (k >= 2048 && tiles(128, 128) * 2 <= dev.sm_count) return VARIANT_CLUSTER_SPLITK_128x128;
   if (tiles(128, 256) >= dev.sm_count / 2) return VARIANT_1CTA_128x256;
   return VARIANT_1CTA_128x128;
@@ -398,9 +405,9 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
     const int num_kb = (k + (kind == 0 ? 64 : 32) - 1) / (kind == 0 ? 64 : 32);
     const long long tiles = (long long)((m + 127) / 128) * ((n + tile_n - 1) / tile_n);
     int s = splits;
-    if (s <= 0) {  // as many slices as fill the GPU once, a power of two, at most 8
+    if (s <= 0) {  // as many slices as fill the GPU once, a power of two, at most 8, each at least 32 K blocks
       s = 8;
-      while (s > 1 && tiles * s > dev->sm_count) s >>= 1;
+      while (s > 1 && (tiles * s > dev->sm_count || num_kb / s < 32)) s >>= 1;
     }
     while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) s >>= 1;  // every slice gets a K block
     if (s != 1 && s != 2 && s != 4 && s != 8)

@@ -239,10 +239,12 @@ __global__ void f32_to_bf16_kernel(const float *__restrict__ src, uint16_t *__re
 // ---- f32 operands split into TF32 pieces ------------------------------------------
 // x = hi + lo with hi = x truncated to TF32 (what the matrix unit would keep,
 // run_gemm_h100.cu:40-44) and lo = x - hi (exact in f32; the unit truncates it
-// again).  Row r of dst holds three K-long pieces: [hi | hi | lo] (order 0, for A)
-// or [hi | lo | hi] (order 1, for B^T), so that one TF32 GEMM over 3K computes
-// hi*hi + hi*lo + lo*hi -- the f32 product up to a 2^-20 relative term -- with f32
-// accumulation.  k % 4 == 0, 16-byte aligned rows.
+// again).  Row r of dst holds three K-long pieces: [hi | lo | hi] (order 0, for A)
+// or [lo | hi | hi] (order 1, for B^T), so that one TF32 GEMM over 3K computes
+// hi*lo + lo*hi + hi*hi -- the f32 product up to a 2^-20 relative term -- with f32
+// accumulation.  The small cross terms come first: the matrix unit's adder drops
+// bits relative to the running sum, so they are summed while it is still small.
+// k % 4 == 0, 16-byte aligned rows.
 __global__ void split_tf32_kernel(const float *__restrict__ src, float *__restrict__ dst, int rows, int k,
                                   int64_t ld_src, int order) {
   const int k4 = k >> 2;
@@ -262,9 +264,9 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, float *__restri
     lo.z = __fsub_rn(x.z, hi.z);
     lo.w = __fsub_rn(x.w, hi.w);
     float *row = dst + (size_t)r * 3 * k + 4 * q;
-    *reinterpret_cast<float4 *>(row) = hi;
-    *reinterpret_cast<float4 *>(row + k) = order == 0 ? hi : lo;
-    *reinterpret_cast<float4 *>(row + 2 * k) = order == 0 ? lo : hi;
+    *reinterpret_cast<float4 *>(row) = order == 0 ? hi : lo;
+    *reinterpret_cast<float4 *>(row + k) = order == 0 ? lo : hi;
+    *reinterpret_cast<float4 *>(row + 2 * k) = hi;
   }
 }
 

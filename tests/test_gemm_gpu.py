@@ -374,8 +374,10 @@ def test_skinny_problem_takes_the_cluster_split_k_path_by_default():
     gemm.fill_normal(a, 3, 0.02, 0)
     gemm.fill_normal(bt, 3, 0.02, 128 * 8192)
     auto = gemm.gemm_bf16(a, bt)
-    explicit = gemm.gemm_bf16(a, bt, flags=gemm.make_flags("cluster_splitk_128x256", splits=4))
+    explicit = gemm.gemm_bf16(a, bt, flags=gemm.make_flags("cluster_splitk_128x128", splits=2))
     assert torch.equal(auto, explicit)
+    unsplit = gemm.gemm_bf16(a, bt, flags=gemm.make_flags("1cta_128x128"))
+    assert not torch.equal(auto, unsplit)           # two K slices, summed once more at the end
     tf = gemm.gemm_tf32(a.float(), bt.float())
     exact = gemm.gemm_exact(a.float(), bt.float(), gemm.INPUT_TF32)
     assert float((tf - exact).abs().max()) <= tc_tol(8192, float(a.float().abs().max()), float(bt.float().abs().max()))
@@ -783,6 +785,55 @@ def test_f32_split_contract():
         gemm.gemm_f32_split(a, a, workspace=torch.empty(16, dtype=torch.uint8, device=DEV))
     with pytest.raises(OxgpuError):
         gemm.gemm_f32_split(torch.zeros(128, 66, device=DEV)[:, :62], torch.zeros(128, 66, device=DEV)[:, :62])
+
+
+def test_launches_can_be_captured_in_a_cuda_graph():
+    """After one eager call (attributes, occupancy query), the buffer entry
+    points only encode maps on the host and launch: a loop of them captures into
+    a CUDA graph, and replays give the eager result.  Covers a CTA-pair kernel, the
+    in-cluster split-K and the affine epilogue."""
+    cases = []
+    for (m, n, k) in [(1024, 5120, 256), (128, 1024, 2048)]:
+        a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+        bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+        gemm.fill_normal(a, 40, 0.5, 0)
+        gemm.fill_normal(bt, 40, 0.5, m * k)
+        bias = torch.arange(n, device=DEV, dtype=torch.float32)
+        eager = gemm.gemm_bf16(a, bt)
+        eager_affine = gemm.gemm_affine(a, bt, None, 2.0, 0.0, bias)
+        outs = [torch.zeros(m, n, device=DEV) for _ in range(3)]
+        cases.append((a, bt, bias, eager, eager_affine, outs))
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for a, bt, bias, _, _, outs in cases:
+            gemm.gemm_bf16(a, bt, outs[0])
+            gemm.gemm_bf16(a, bt, outs[1])
+            gemm.gemm_affine(a, bt, outs[2], 2.0, 0.0, bias)
+    for _ in range(3):
+        for *_, outs in cases:
+            for o in outs:
+                o.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        for _, _, _, eager, eager_affine, outs in cases:
+            assert torch.equal(outs[0], eager) and torch.equal(outs[1], eager)
+            assert torch.equal(outs[2], eager_affine)
+
+
+def test_single_tile_row_problems_do_not_take_tall_tiles():
+    """M = 128 against a wide N: a 512-row pair tile would be three quarters
+    padding; the library must pick a 128-row tile (same bits as asking for it)."""
+    a = torch.empty(128, 512, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(28672, 512, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 6, 1.0, 0)
+    gemm.fill_normal(bt, 6, 1.0, 128 * 512)
+    before = gemm.launch_count()
+    auto = gemm.gemm_bf16(a, bt)
+    assert gemm.launch_count() == before + 1
+    assert torch.equal(auto, gemm.gemm_bf16(a, bt, flags=gemm.make_flags("1cta_128x128")))
+    exact = gemm.gemm_exact(a, bt, gemm.INPUT_BF16)
+    assert float((auto - exact).abs().max()) <= strict_tol(512, float(a.float().abs().max()), float(bt.float().abs().max()))
 
 
 def test_launch_count_increases():
