@@ -64,6 +64,15 @@ def blocks_to_row_major(gathered: torch.Tensor) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(m, world * w).contiguous()
 
 
+def fanout_destinations(bases: list[int], n0: int, element_bytes: int = 4) -> list[int]:
+    """Device addresses the fan-out GEMM of the rank owning columns [n0, ...)
+    writes to: the first element of its column window in every rank's row-major
+    C (`bases[i]` = address of rank i's C in this process)."""
+    if n0 < 0 or (n0 * element_bytes) % 16:
+        raise ValueError("a column window must start on a 16-byte boundary")
+    return [b + n0 * element_bytes for b in bases]
+
+
 def peers_alive(group=None, timeout_s: float = 5.0) -> bool:
     """Host-side liveness check before a launch that writes into other ranks'
     memory: True if every rank of the group reached this call within the
@@ -163,7 +172,7 @@ class FusedGatherGemm:
             raise RuntimeError("a rank of the group did not answer: nothing was launched")
         if self.width == 0:
             return
-        dests = [base + self.n0 * 4 for base in self._dest_base]
+        dests = fanout_destinations(self._dest_base, self.n0)
         self._gemm.gemm_fanout(a, bt_shard, dests, ldc=self.n, flags=self.flags)
 
     def finish(self) -> torch.Tensor:

@@ -175,3 +175,13 @@ def test_peers_alive_reports_a_departed_rank():
         r, first, second = results.get()
         got[r] = (first, second)
     assert got[1][0] is True and got[0] == (True, False), got
+
+
+def test_fanout_destination_windows():
+    bases = [0x7000_0000_0000, 0x7100_0000_0000, 0x7200_0000_0000]
+    n = 2304
+    for rank, (n0, n1) in enumerate(sharded.column_partition(n, 3)):
+        d = sharded.fanout_destinations(bases, n0)
+        assert d == [b + 4 * n0 for b in bases] and all(x % 16 == 0 for x in d)
+    with pytest.raises(ValueError):
+        sharded.fanout_destinations(bases, 3)       # 12 bytes into a row: not 16-byte aligned
