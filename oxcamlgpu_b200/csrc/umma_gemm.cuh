@@ -108,6 +108,17 @@ struct GemmParamsFanout : GemmParams {
   int n_dests;
 };
 
+// Tile t of the walk -> (tile row, tile column): the reference's grouped order
+// (common.hpp grouped_tile), with the columns of every other group of tile rows
+// walked in reverse.  At the turn from one group to the next the B^T panels that
+// were used last are used first, while they are still in L2 (16384 x 16384 x
+// 8192 with a cold L2: 3.13 -> 2.97 ms; no effect at 8192^3, where a group is
+// a third of the problem).  Which SM computes a tile does not change its value.
+__device__ __forceinline__ void tile_coords(const GemmParams &p, int t, int *tm, int *tn) {
+  grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, tm, tn);
+  if ((*tm / p.group_m) & 1) *tn = p.tiles_n - 1 - *tn;
+}
+
 struct WaitCtx {
   unsigned long long budget_ns;
   volatile uint32_t *abort_flag;  // shared memory, one per CTA
@@ -115,13 +126,23 @@ struct WaitCtx {
 
 // Bounded mbarrier wait.  Returns false if the budget ran out (or another
 // role of this CTA already gave up).
+// max_nap_ns > 0: sleep between polls, 32 ns doubling up to max_nap_ns.  For waits
+// that normally last most of a tile (the epilogue waiting for an accumulator):
+// eight warps per SM polling flat out cost about 1 % of SM clock under the
+// power cap; a 256 ns ceiling gives that back and delays the wake-up by less
+// than the head start the issuer gives the epilogue.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx &ctx,
-                                             uint32_t kind, uint32_t detail) {
+                                             uint32_t kind, uint32_t detail, uint32_t max_nap_ns = 0) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
+  uint32_t nap = 32;
   while (true) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (max_nap_ns) {
+      __nanosleep(nap);
+      if (nap < max_nap_ns) nap <<= 1;
+    }
     if ((++spins & 0xffu) == 0) {
       if (*ctx.abort_flag) return false;
       if (ptx::globaltimer_ns() - t0 > ctx.budget_ns) {
@@ -391,7 +412,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         const int kb_begin = sp * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
         int tm, tn;
-        grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+        tile_coords(p, t, &tm, &tn);
         const int a_row0 = tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA;
         const int b_row0 = tn * (NI * BN) + (int)cta_rank * (NI * B_ROWS);
         for (int kb = kb_begin; kb < kb_end; kb++) {
@@ -588,7 +609,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       const uint32_t set_phase = (uint32_t)(local_tile / SETS) & 1u;
       const int unit = set * U + mi;
       int tm, tn;
-      grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+      tile_coords(p, t, &tm, &tn);
       const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
                         (MI == 2 ? mi * 128 : 0) + quad * 32;
       // first column in C of this warp's chunk c (32 accumulator columns)
@@ -601,7 +622,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       // warp parks at the shuffle instead of polling the barrier
       uint32_t got = 0;
       if (lane == 0)
-        got = bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w) ? 1u : 0u;
+        got = bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w, 256u) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) {
         ok = false;
@@ -725,7 +746,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         const int rank = (int)(blockIdx.x % (unsigned)S);
         const int t = (int)(blockIdx.x / (unsigned)S);
         int tm, tn;
-        grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, &tm, &tn);
+        tile_coords(p, t, &tm, &tn);
         const int pieces_per_row = (BN / 4) / S;  // this CTA's column range, in 16-byte pieces
         const int row0 = tm * 128, col0 = tn * BN;
         const CrossSliceSum job{smem_base, BN * 4, rank * pieces_per_row, pieces_per_row, row0, col0,
