@@ -274,6 +274,12 @@ OXGPU_API int oxgpu_b200_gemm_bf16_affine(const uint16_t *a, const uint16_t *bt,
                                           int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
                                           const oxgpu_epilogue *epilogue, unsigned flags,
                                           void *stream);
+/* The same with bf16 C (bf16 inputs): the affine steps in f32, then one rounding
+ * to nearest even.  c_in stays f32.  ldc a multiple of 8. */
+OXGPU_API int oxgpu_b200_gemm_bf16_out16_affine(const uint16_t *a, const uint16_t *bt, uint16_t *c,
+                                                int m, int n, int k, int64_t lda, int64_t ldb,
+                                                int64_t ldc, const oxgpu_epilogue *epilogue,
+                                                unsigned flags, void *stream);
 OXGPU_API int oxgpu_b200_gemm_tf32_affine(const float *a, const float *bt, float *c, int m, int n,
                                           int k, int64_t lda, int64_t ldb, int64_t ldc,
                                           const oxgpu_epilogue *epilogue, unsigned flags,

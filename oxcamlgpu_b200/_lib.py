@@ -89,6 +89,8 @@ def lib() -> ctypes.CDLL:
                                        ctypes.c_uint, c_void_p, sz, c_void_p], c_int),
         "oxgpu_b200_gemm_bf16_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                          ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
+        "oxgpu_b200_gemm_bf16_out16_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
+                                               ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_gemm_tf32_affine": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                          ctypes.POINTER(EpilogueStruct), ctypes.c_uint, c_void_p], c_int),
         "oxgpu_b200_shared_alloc": ([sz, ctypes.POINTER(c_void_p), ctypes.c_char_p], c_int),

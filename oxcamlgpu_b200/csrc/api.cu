@@ -22,7 +22,7 @@ namespace oxgpu {
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kKinds = 7;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out, 5 / 6 = affine
+constexpr int kKinds = 8;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4 = bf16 / tf32 fan-out, 5 / 6 = affine, 7 = affine with bf16 C
 constexpr int kVariants = 12;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
@@ -204,6 +204,16 @@ const void *affine_kernel_for(int kind, int variant) {
   return nullptr;
 }
 
+// bf16 inputs, affine epilogue, bf16 C.
+const void *affine_out16_kernel_for(int variant) {
+  switch (variant) {
+    case VARIANT_1CTA_128x128: return (const void *)umma_gemm_kernel<0, 128, 128, 1, true, false, 1, true>;
+    case VARIANT_2CTA_256x256: return (const void *)umma_gemm_kernel<0, 128, 256, 2, true, false, 1, true>;
+    case VARIANT_2CTA_512x256: return (const void *)umma_gemm_kernel<0, 256, 256, 2, true, false, 1, true>;
+  }
+  return nullptr;
+}
+
 unsigned long long wait_budget_ns() {
   static unsigned long long v = [] {
     const char *e = std::getenv("OXGPU_WAIT_BUDGET_MS");
@@ -233,10 +243,11 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
                 cudaStream_t stream) {
   const VariantShape shape = variant_shape(plan.variant);
   const void *fn = plan.fanout   ? fanout_kernel_for(plan.kind, plan.variant)
+                   : plan.affine && plan.out16 ? affine_out16_kernel_for(plan.variant)
                    : plan.affine ? affine_kernel_for(plan.kind, plan.variant)
                                  : kernel_for(plan.kind, plan.variant, plan.out16);
   if (!fn || shape.cta_group == 0) return fail(OXGPU_E_INVALID_ARG, "unknown kernel variant");
-  const int attr_kind = plan.fanout ? 3 + plan.kind : plan.affine ? 5 + plan.kind : (plan.out16 ? 2 : plan.kind);
+  const int attr_kind = plan.fanout ? 3 + plan.kind : plan.affine ? (plan.out16 ? 7 : 5 + plan.kind) : (plan.out16 ? 2 : plan.kind);
   int stages = plan.stages;
   const int most = variant_max_stages(plan.variant);
   if (stages <= 0 || stages > most) stages = most;
@@ -543,11 +554,13 @@ int gemm_fanout(int kind, const void *a, const void *bt, float *const *dests, in
 
 // C = alpha * (A B) + beta * C_in + bias in the GEMM's own epilogue.
 int gemm_affine(int kind, const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
-                int64_t ldb, int64_t ldc, const oxgpu_epilogue *ep, unsigned flags, cudaStream_t stream) {
+                int64_t ldb, int64_t ldc, const oxgpu_epilogue *ep, unsigned flags, cudaStream_t stream,
+                bool out16 = false) {
   const int esize = kind == 0 ? 2 : 4;
   if (!ep) return fail(OXGPU_E_INVALID_ARG, "null epilogue description");
   int st = check_buffers(a, bt, c, m, n, k, lda, ldb, ldc, esize);
   if (st) return st;
+  if (out16 && (ldc * 2) % 16) return fail(OXGPU_E_ALIGN, "bf16 C needs ldc to be a multiple of 8");
   if (ep->bias && !aligned16(ep->bias)) return fail(OXGPU_E_ALIGN, "bias must be 16-byte aligned");
   if (ep->beta != 0.0f) {
     if (!ep->c_in) return fail(OXGPU_E_INVALID_ARG, "beta != 0 needs c_in");
@@ -559,7 +572,7 @@ int gemm_affine(int kind, const void *a, const void *bt, float *c, int m, int n,
   if ((st = current_device(&dev_index, &dev))) return st;
   int variant = (int)(flags & 0xffu);
   if (variant == VARIANT_AUTO) variant = choose_large_tile_variant(*dev, m, n);
-  if (!affine_kernel_for(kind, variant))
+  if (out16 ? !affine_out16_kernel_for(variant) : !affine_kernel_for(kind, variant))
     return fail(OXGPU_E_INVALID_ARG, "this variant has no affine-epilogue kernel (use 1cta_128x128, 2cta_256x256 or 2cta_512x256)");
   const VariantShape shape = variant_shape(variant);
   const int kbe = kind == 0 ? 64 : 32;
@@ -567,6 +580,7 @@ int gemm_affine(int kind, const void *a, const void *bt, float *c, int m, int n,
   const int reorder_field = (int)((flags >> 28) & 0xfu);
   plan.reorder_kb = reorder_field == 0 ? -1 : (reorder_field == 15 ? 0 : reorder_field);
   plan.affine = true;
+  plan.out16 = out16;
   GemmParams p;
   std::memset(&p, 0, sizeof p);
   p.a_box_rows = shape.cta_a_rows;
@@ -575,7 +589,9 @@ int gemm_affine(int kind, const void *a, const void *bt, float *c, int m, int n,
     return st;
   if ((st = encode_2d(&p.map_b, bt, esize, (uint64_t)k, (uint64_t)n, (uint64_t)ldb * esize, kbe, p.b_box_rows)))
     return st;
-  if ((st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32))) return st;
+  if (out16) st = encode_2d(&p.map_c, c, 2, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 2, 64, 32);
+  else st = encode_2d(&p.map_c, c, 4, (uint64_t)n, (uint64_t)m, (uint64_t)ldc * 4, 32, 32);
+  if (st) return st;
   p.c_ptr = c;
   p.c_ld = ldc;
   p.c_rows = m;
@@ -868,6 +884,14 @@ int oxgpu_b200_gemm_bf16_affine(const uint16_t *a, const uint16_t *bt, float *c,
                                 int64_t lda, int64_t ldb, int64_t ldc, const oxgpu_epilogue *epilogue,
                                 unsigned flags, void *stream) {
   return oxgpu::gemm_affine(0, a, bt, c, m, n, k, lda, ldb, ldc, epilogue, flags, (cudaStream_t)stream);
+}
+
+int oxgpu_b200_gemm_bf16_out16_affine(const uint16_t *a, const uint16_t *bt, uint16_t *c, int m, int n, int k,
+                                      int64_t lda, int64_t ldb, int64_t ldc, const oxgpu_epilogue *epilogue,
+                                      unsigned flags, void *stream) {
+  // (check_buffers only looks at the pointer and the leading dimension of C)
+  return oxgpu::gemm_affine(0, a, bt, reinterpret_cast<float *>(c), m, n, k, lda, ldb, ldc, epilogue, flags,
+                            (cudaStream_t)stream, true);
 }
 
 int oxgpu_b200_gemm_tf32_affine(const float *a, const float *bt, float *c, int m, int n, int k, int64_t lda,

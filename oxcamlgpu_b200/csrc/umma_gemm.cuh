@@ -289,13 +289,13 @@ __device__ __forceinline__ void affine_chunk(uint32_t (&v)[32], const GemmParams
 // (the reference's 256-row B^T box): UMMA `ni` of a K step reads rows
 // [ni * BN/2, (ni + 1) * BN/2) of both CTAs' stages, so accumulator column j of
 // block ni is tile column (j / (BN/2)) * BN + ni * BN/2 + j % (BN/2).
-// AFFINE: the f32 epilogue applies alpha, beta * C_in and a bias row (affine_chunk).
+// AFFINE: the epilogue applies alpha, beta * C_in and a bias row (affine_chunk) in
+// f32, before the rounding to bf16 when OUT16 is set as well.
 template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1,
           bool AFFINE = false>
 __global__ void __launch_bounds__(kThreadsPerCta, 1)
 umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmParamsFanout, GemmParams>::type p) {
   static_assert(!(FANOUT && OUT16), "the fan-out epilogue writes f32");
-  static_assert(!(AFFINE && OUT16), "the affine epilogue writes f32");
   // A CTA owns BM_CTA rows of the tile as MI blocks of 128 rows (one UMMA each
   // per K step, all sharing the staged B^T rows).  Block `mi` of accumulator
   // set `set` is one hand-off unit between the issuer and the epilogue.
@@ -708,6 +708,10 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c2 * 64 + 32), vb);
           ptx::tmem_ld_wait();
           if (c2 + 1 == CHUNKS_PER_GROUP / 2) release_unit();
+          if constexpr (AFFINE) {  // in f32, before the one rounding to bf16
+            affine_chunk(va, p, c_row + lane, chunk_col(2 * c2));
+            affine_chunk(vb, p, c_row + lane, chunk_col(2 * c2) + 32);
+          }
           if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();
 #pragma unroll

@@ -162,7 +162,14 @@ def gemm_affine(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None
     if kind is None:
         raise ValueError("operands must be bf16 or f32")
     m, n, k = _check_operands(a, bt, a.dtype)
-    c = _out(c, m, n, a.device)
+    out16 = c is not None and c.dtype == torch.bfloat16      # bf16 C: pass a bf16 tensor to write into
+    if out16:
+        if kind != "bf16" or c.stride(1) != 1 or tuple(c.shape) != (m, n):
+            raise ValueError("bf16 C needs bf16 operands and a [M,N] tensor with unit column stride")
+        if beta != 0.0 and c_in is None:
+            raise ValueError("with bf16 C, c_in (f32) must be given when beta != 0")
+    else:
+        c = _out(c, m, n, a.device)
     if beta != 0.0 and c_in is None:
         c_in = c
     if bias is not None and (bias.dtype != torch.float32 or tuple(bias.shape) != (n,) or not bias.is_contiguous()):
@@ -172,7 +179,8 @@ def gemm_affine(a: torch.Tensor, bt: torch.Tensor, c: torch.Tensor | None = None
     ep = EpilogueStruct(alpha, beta, bias.data_ptr() if bias is not None else None,
                         c_in.data_ptr() if c_in is not None else None,
                         c_in.stride(0) if c_in is not None else 0)
-    fn = lib().oxgpu_b200_gemm_bf16_affine if kind == "bf16" else lib().oxgpu_b200_gemm_tf32_affine
+    fn = (lib().oxgpu_b200_gemm_bf16_out16_affine if out16 else
+          lib().oxgpu_b200_gemm_bf16_affine if kind == "bf16" else lib().oxgpu_b200_gemm_tf32_affine)
     check(fn(a.data_ptr(), bt.data_ptr(), c.data_ptr(), m, n, k, a.stride(0), bt.stride(0), c.stride(0),
              ctypes.byref(ep), flags, ctypes.c_void_p(_stream(stream))))
     return c

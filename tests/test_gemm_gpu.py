@@ -701,6 +701,27 @@ def test_affine_epilogue(variant, alpha, beta, use_bias):
     assert torch.equal(c, expect)
 
 
+@pytest.mark.parametrize("variant", FANOUT_VARIANTS)
+def test_affine_epilogue_with_bf16_output(variant):
+    """bias (and alpha, beta * C_in) applied in f32, then ONE rounding to bf16:
+    equal to rounding the f32 affine kernel's result."""
+    m, n, k = 300, 1288, 320
+    rng = np.random.default_rng(19)
+    a_bits, bt_bits = rand_bf16(rng, m, k), rand_bf16(rng, n, k)
+    a, bt = bf16_tensor(a_bits), bf16_tensor(bt_bits)
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(DEV)
+    c_in = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(DEV)
+    flags = gemm.make_flags(variant)
+    for alpha, beta in ((1.0, 0.0), (0.5, -2.0)):
+        f32 = gemm.gemm_affine(a, bt, None, alpha, beta, bias, c_in, flags=flags)
+        pad = torch.full((m + 2, n + 16), float("nan"), device=DEV, dtype=torch.bfloat16)
+        c16 = pad[1:m + 1, 8:n + 8]
+        gemm.gemm_affine(a, bt, c16, alpha, beta, bias, c_in, flags=flags)
+        assert torch.equal(c16, f32.to(torch.bfloat16))
+        assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
+        assert torch.isnan(pad[:, :8]).all() and torch.isnan(pad[:, n + 8:]).all()
+
+
 def test_affine_epilogue_tf32_and_beta_zero_ignores_c_in():
     m, n, k = 512, 768, 256
     a = torch.empty(m, k, device=DEV)
