@@ -168,7 +168,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": metric_name(args.workload), "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "strong" if args.workload == "cfg5" else "weak", "vs_baseline": None,
         "dtype": "bf16" if kind == "bf16" else "tf32", "data": "synthetic",
         "config": dict(workload_config(args.workload, args.gpus), variant=args.variant),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
