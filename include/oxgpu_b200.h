@@ -168,7 +168,8 @@ OXGPU_API int oxgpu_b200_encode_tmap_2d(void *map_out, const void *device_ptr, i
  * n % bn == 0, k % BK == 0 like the reference (bench/bench.py:247-250); BK is
  * 32 for the f32 entries and 64 for gemm_bf16_fast.  The library serves every
  * name with a 128-row (or 256-row) tcgen05 tile, issuing the per-stage loads in
- * units of the caller's boxes; bm=64 entries therefore also need m % 128 == 0.
+ * units of the caller's boxes (a bm=64 entry by two 64-row loads per 128-row
+ * tile; rows past M are zero-filled on load and clipped on store).
  * Replaces cuLaunchKernel(fn, n/bn, m/bm, 1, threads, ...). */
 OXGPU_API int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uint64_t c,
                                    int m, int n, int k, void *stream);
@@ -353,6 +354,98 @@ OXGPU_API int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16
                                                  int m, int n, int k, int64_t lda, int64_t ldb,
                                                  int64_t ldc, int splits, void *stream);
 
+/* ---- multi-GPU driver ------------------------------------------------------
+ * One process drives up to 8 GPUs of one machine: B^T and C are split by
+ * columns (contiguous row blocks of B^T), A is replicated, every device runs
+ * the single-GPU kernel on its shard, and nothing crosses NVLink unless a
+ * replicated C is asked for.  The reference has no multi-GPU path, so these
+ * have no counterpart there; the launcher they sit beside drives one device
+ * from one host thread (test/hardware/run_gemm_h100.cu:100-108,183-186).
+ * A handle owns one stream, three events and one host thread per device; peer
+ * access between its devices is enabled once at creation.  Calls on one handle
+ * are not reentrant: issue them from one thread at a time. */
+typedef struct oxgpu_mg oxgpu_mg;
+
+#define OXGPU_MG_COLUMN_ALIGN 256 /* shard widths are multiples of the widest tile */
+
+/* The column partition the driver uses, as a pure host function: `parts`
+ * contiguous ranges [n0[r], n1[r]) of whole `align`-column blocks, block counts
+ * differing by at most one (the first ranges take the extra blocks), the last
+ * non-empty range carrying the ragged tail; ranges may be empty when there are
+ * fewer blocks than parts. */
+OXGPU_API int oxgpu_b200_mg_column_partition(int n, int parts, int align, int *n0, int *n1);
+
+/* devices: CUDA device ordinals (NULL = 0 .. ngpu-1), no repeats.  The caller's
+ * current device is left as it was. */
+OXGPU_API int oxgpu_b200_mg_create(int ngpu, const int *devices, oxgpu_mg **out);
+OXGPU_API int oxgpu_b200_mg_destroy(oxgpu_mg *mg); /* waits for the handle's streams first */
+OXGPU_API int oxgpu_b200_mg_device_count(const oxgpu_mg *mg);
+OXGPU_API int oxgpu_b200_mg_device(const oxgpu_mg *mg, int index); /* CUDA ordinal of device `index` */
+OXGPU_API int oxgpu_b200_mg_peer_access(const oxgpu_mg *mg);       /* 1: every device can store into every other's memory */
+
+enum {
+  OXGPU_MG_GATHER_NONE = 0,  /* C stays sharded */
+  /* ncclAllGather of the shards over NVLink, then a re-interleave pass on every
+   * device: c_full[i] is the row-major C[M,N].  Needs equal shard widths
+   * (N a multiple of 256 * devices) and M*N*4 bytes of scratch per device, which
+   * the handle allocates on first use and keeps. */
+  OXGPU_MG_GATHER_NCCL = 1,
+  /* One kernel: each device's GEMM stores every tile into all devices' row-major
+   * C[M,N] as it is produced (plain peer stores over NVLink; no peer loads, no
+   * multicast).  c_shard is not used.  Needs peer access. */
+  OXGPU_MG_GATHER_FUSED = 2,
+  /* ncclAllGather only: c_full[i] is block-column-major [devices][M][N/devices],
+   * the layout NCCL's contiguous chunks give. */
+  OXGPU_MG_GATHER_NCCL_BLOCKS = 3
+};
+
+/* C[:, n0_d:n1_d] = A * B[:, n0_d:n1_d] on device d, for the partition above.
+ * a_repl[d]: A[M,K] bf16 row-major in device d's memory; bt_shard[d]: rows
+ * [n0_d, n1_d) of B^T[N,K]; c_shard[d]: f32 [M, n1_d-n0_d], dense.  All dense
+ * (leading dimension = row length) and 16-byte aligned.  c_full[d]: f32 M*N in
+ * device d's memory, used when gather_c != NONE.  flags as for
+ * oxgpu_b200_gemm_bf16.  Returns once every device's work is enqueued on the
+ * handle's streams; oxgpu_b200_mg_sync waits for it.  The pointer arrays need
+ * only live until the call returns. */
+OXGPU_API int oxgpu_b200_mg_gemm_bf16(oxgpu_mg *mg, const uint16_t *const *a_repl,
+                                      const uint16_t *const *bt_shard, float *const *c_shard, int m,
+                                      int n, int k, int gather_c, float *const *c_full,
+                                      unsigned flags);
+OXGPU_API int oxgpu_b200_mg_sync(oxgpu_mg *mg);
+
+/* Device time of the last call, per device (arrays of device_count floats,
+ * either may be NULL): total_ms from its first to its last operation, gemm_ms
+ * the GEMM alone (the rest is the gather).  Waits for the call to finish. */
+OXGPU_API int oxgpu_b200_mg_elapsed_ms(oxgpu_mg *mg, float *total_ms, float *gemm_ms);
+
+/* Host-operand form: A[M,K], B^T[N,K] and C in HOST memory (pinned for full
+ * speed).  Every device uploads A and its own rows of B^T, computes its columns
+ * block of rows by block of rows and downloads them while the next block comes
+ * up.  c_layout: row-major C[M,N] (each device writes its column window, pitch
+ * N), or OXGPU_MG_HOST_C_BLOCKS: device d's columns as a contiguous [M][w_d]
+ * block at element offset n0_d * M (one long run per device instead of M short
+ * ones).  Synchronises: C is complete on the host when it returns.  Device
+ * staging buffers are allocated on first use and kept by the handle. */
+enum { OXGPU_MG_HOST_C_ROW_MAJOR = 0, OXGPU_MG_HOST_C_BLOCKS = 1 };
+OXGPU_API int oxgpu_b200_mg_gemm_bf16_host(oxgpu_mg *mg, const uint16_t *a_host,
+                                           const uint16_t *bt_host, float *c_host, int m, int n,
+                                           int k, int c_layout, unsigned flags);
+
+/* Device memory and copies for callers with no other CUDA binding (set-up, not
+ * the hot path).  `index` counts the handle's devices.  _copy is synchronous. */
+enum { OXGPU_MG_COPY_TO_DEVICE = 0, OXGPU_MG_COPY_TO_HOST = 1 };
+OXGPU_API int oxgpu_b200_mg_alloc(oxgpu_mg *mg, int index, size_t bytes, void **ptr);
+OXGPU_API int oxgpu_b200_mg_free(oxgpu_mg *mg, int index, void *ptr);
+OXGPU_API int oxgpu_b200_mg_copy(oxgpu_mg *mg, int index, void *dst, const void *src, size_t bytes,
+                                 int direction);
+
+/* Pinned host memory placed on the NUMA node `device` hangs off (device < 0: no
+ * placement), for the host-operand entry points: on a two-socket machine a
+ * buffer on the far socket crosses the socket interconnect on its way to the
+ * GPU.  Portable across devices.  Free with the same byte count. */
+OXGPU_API int oxgpu_b200_host_alloc(size_t bytes, int device, void **ptr);
+OXGPU_API int oxgpu_b200_host_free(void *ptr, size_t bytes);
+
 /* Exact GEMM on CUDA cores: one f32 accumulator per output, k ascending, a
  * rounded multiply then a rounded add (never fused) -- the arithmetic of the
  * host reference loop (test/hardware/run_gemm_h100.cu:150-162), so the result
@@ -384,7 +477,11 @@ OXGPU_API int oxgpu_b200_transpose_f32_to_bf16(const float *b, uint16_t *bt, int
  * pageable).  Uploads the operands, runs gemm_bf16 and downloads C, pipelined
  * over row blocks of A/C on internal streams; returns after C is complete on
  * the host (this call synchronises).  Device staging buffers are allocated on
- * first use and cached per device; oxgpu_b200_release_staging frees them. */
+ * first use and cached per device, with three streams and their events;
+ * oxgpu_b200_release_staging frees all of it.  If a step fails, the work already
+ * queued is waited for before the error is returned, so the caller's buffers are
+ * no longer in use when the call returns.  A device-side wait that timed out is
+ * reported by the next oxgpu_b200_device_status. */
 OXGPU_API int oxgpu_b200_gemm_bf16_host(const uint16_t *a_host, const uint16_t *bt_host,
                                         float *c_host, int m, int n, int k, unsigned flags);
 OXGPU_API int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *c_host,

@@ -99,6 +99,25 @@ def lib() -> ctypes.CDLL:
         "oxgpu_b200_shared_free": ([c_void_p], c_int),
         "oxgpu_b200_gemm_bf16_splitk_static": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64,
                                                 i64, i64, c_int, c_void_p], c_int),
+        "oxgpu_b200_mg_column_partition": ([c_int, c_int, c_int, intp, intp], c_int),
+        "oxgpu_b200_mg_create": ([c_int, intp, ctypes.POINTER(c_void_p)], c_int),
+        "oxgpu_b200_mg_destroy": ([c_void_p], c_int),
+        "oxgpu_b200_mg_device_count": ([c_void_p], c_int),
+        "oxgpu_b200_mg_device": ([c_void_p, c_int], c_int),
+        "oxgpu_b200_mg_peer_access": ([c_void_p], c_int),
+        "oxgpu_b200_mg_gemm_bf16": ([c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
+                                     ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int,
+                                     ctypes.POINTER(c_void_p), ctypes.c_uint], c_int),
+        "oxgpu_b200_mg_sync": ([c_void_p], c_int),
+        "oxgpu_b200_mg_elapsed_ms": ([c_void_p, ctypes.POINTER(ctypes.c_float),
+                                      ctypes.POINTER(ctypes.c_float)], c_int),
+        "oxgpu_b200_mg_gemm_bf16_host": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          ctypes.c_uint], c_int),
+        "oxgpu_b200_mg_alloc": ([c_void_p, c_int, sz, ctypes.POINTER(c_void_p)], c_int),
+        "oxgpu_b200_mg_free": ([c_void_p, c_int, c_void_p], c_int),
+        "oxgpu_b200_mg_copy": ([c_void_p, c_int, c_void_p, c_void_p, sz, c_int], c_int),
+        "oxgpu_b200_host_alloc": ([sz, c_int, ctypes.POINTER(c_void_p)], c_int),
+        "oxgpu_b200_host_free": ([c_void_p, sz], c_int),
         "oxgpu_b200_gemm_exact": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,
                                    c_int, c_void_p], c_int),
         "oxgpu_b200_transpose": ([c_void_p, c_void_p, c_int, c_int, c_int, c_void_p], c_int),

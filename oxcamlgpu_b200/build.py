@@ -13,7 +13,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "liboxgpu_b200.so")
-SOURCES = ["api.cu", "catalog.cpp"]
+SOURCES = ["api.cu", "mg.cu", "catalog.cpp"]
 HEADERS = ["common.hpp", "ptx.cuh", "umma_gemm.cuh", "util_kernels.cuh",
            os.path.join("..", "..", "include", "oxgpu_b200.h")]
 

@@ -35,11 +35,15 @@ struct Staging {
   bool events = false;
 };
 
+// Lazily filled per-device facts.  Host threads may race to fill them (the
+// values written are the same whoever wins), so every field that is read
+// outside g_mutex is an atomic; `ready` is published with release ordering
+// after sm_count.
 struct DeviceState {
-  bool ready = false;
-  int sm_count = 0;
-  bool attr_set[kKinds][kVariants] = {};
-  int max_clusters[kKinds][kVariants] = {};
+  std::atomic<bool> ready{false};
+  std::atomic<int> sm_count{0};
+  std::atomic<bool> attr_set[kKinds][kVariants] = {};
+  std::atomic<int> max_clusters[kKinds][kVariants] = {};
   Staging staging;
 };
 
@@ -51,7 +55,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn g_encode = nullptr;
+std::atomic<EncodeTiledFn> g_encode{nullptr};
 
 int cuda_fail(cudaError_t e, const char *what) {
   return fail((int)e, std::string(what) + ": " + cudaGetErrorName(e) + ": " + cudaGetErrorString(e));
@@ -64,9 +68,9 @@ int cuda_fail(cudaError_t e, const char *what) {
   } while (0)
 
 int resolve_driver() {
-  if (g_encode) return OXGPU_OK;
+  if (g_encode.load(std::memory_order_acquire)) return OXGPU_OK;
   std::lock_guard<std::mutex> lock(g_mutex);
-  if (g_encode) return OXGPU_OK;
+  if (g_encode.load(std::memory_order_acquire)) return OXGPU_OK;
   void *fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   cudaError_t e = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000,
@@ -75,7 +79,7 @@ int resolve_driver() {
     cudaGetLastError();
     return fail(OXGPU_E_NO_DRIVER, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   }
-  g_encode = (EncodeTiledFn)fn;
+  g_encode.store((EncodeTiledFn)fn, std::memory_order_release);
   return OXGPU_OK;
 }
 
@@ -83,16 +87,18 @@ int current_device(int *dev, DeviceState **state) {
   OX_CUDA(cudaGetDevice(dev));
   if (*dev < 0 || *dev >= kMaxDevices) return fail(OXGPU_E_INVALID_ARG, "device index out of range");
   DeviceState &s = g_dev[*dev];
-  if (!s.ready) {
+  if (!s.ready.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (!s.ready) {
-      OX_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, *dev));
+    if (!s.ready.load(std::memory_order_acquire)) {
+      int sms = 0;
+      OX_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, *dev));
+      s.sm_count.store(sms, std::memory_order_relaxed);
       int major = 0;
       OX_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, *dev));
       if (major != 10)
         return fail(OXGPU_E_INVALID_ARG,
                     "this library is built for sm_100a only; the current device is not a B200-class GPU");
-      s.ready = true;
+      s.ready.store(true, std::memory_order_release);
     }
   }
   *state = &s;
@@ -112,7 +118,7 @@ int encode_2d(CUtensorMap *map, const void *ptr, int element_bytes, uint64_t dim
   cuuint64_t strides[1] = {stride1_bytes};
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+  CUresult r = g_encode.load(std::memory_order_acquire)(map, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promotion,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -283,10 +289,10 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   p.hint_c = 1;
   p.wait_budget_ns = wait_budget_ns();
 
-  bool &attr = dev.attr_set[attr_kind][plan.variant];
-  if (!attr) {
+  std::atomic<bool> &attr = dev.attr_set[attr_kind][plan.variant];
+  if (!attr.load(std::memory_order_acquire)) {
     OX_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem));
-    attr = true;
+    attr.store(true, std::memory_order_release);
   }
 
   const long long work = (long long)p.tiles_m * p.tiles_n * p.splits;
@@ -304,13 +310,15 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    int &maxc = dev.max_clusters[attr_kind][plan.variant];
+    std::atomic<int> &cached = dev.max_clusters[attr_kind][plan.variant];
+    int maxc = cached.load(std::memory_order_relaxed);
     if (maxc == 0) {
       cfg.gridDim = dim3(2 * (dev.sm_count / 2), 1, 1);
       int nc = 0;
       OX_CUDA(cudaOccupancyMaxActiveClusters(&nc, fn, &cfg));
       if (nc <= 0) return fail(OXGPU_E_INVALID_ARG, "no CTA pair of this variant fits on the device");
       maxc = nc;
+      cached.store(nc, std::memory_order_relaxed);
     }
     long long clusters = work < maxc ? work : maxc;
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
@@ -325,7 +333,8 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     cfg.gridDim = dim3((unsigned)work, 1, 1);
     p.cluster_reduce = 1;
   } else {
-    long long ctas = work < dev.sm_count ? work : dev.sm_count;
+    const int sms = dev.sm_count;
+    long long ctas = work < sms ? work : sms;
     cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   }
   void *args[1] = {(void *)&p};
@@ -669,6 +678,20 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
   const int na = (m + a_rows - 1) / a_rows, nb = (n + b_rows - 1) / b_rows;
   const size_t row_bytes = (size_t)k * esize;
   int a_up = 0, b_up = 0, ev = 0;  // blocks uploaded so far; next event slot
+  // On any error the copies and kernels already queued are waited for before the
+  // call returns: they read the caller's A and B^T and write the caller's C, and
+  // the staging buffers must be idle before the next call reuses them.
+  struct Drain {
+    Staging &s;
+    bool armed = true;
+    ~Drain() {
+      if (!armed) return;
+      cudaStreamSynchronize(s.in);
+      cudaStreamSynchronize(s.compute);
+      cudaStreamSynchronize(s.out);
+      cudaGetLastError();
+    }
+  } drain{s};
 
   // compute C[r0:r0+rows, c0:c0+cols] on the device and send it down
   auto emit = [&](int r0, int rows, int c0, int cols, cudaEvent_t ready) -> int {
@@ -716,6 +739,7 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
   }
   OX_CUDA(cudaStreamSynchronize(s.out));
   OX_CUDA(cudaStreamSynchronize(s.in));
+  drain.armed = false;
   return OXGPU_OK;
 }
 
@@ -766,8 +790,10 @@ int oxgpu_b200_gemm_tmap(const char *name, uint64_t a_tmap, uint64_t b_tmap, uin
   //    entry's own tile shape when M or N is not a multiple of 256.
   // A larger tile is only taken when it still gives every SM (or SM pair) a
   // tile; small problems keep the entry's own shape so more SMs have work.
-  if (m % variant_shape(e->variant).tile_m)
-    return fail(OXGPU_E_SHAPE, "this entry is served by a 128-row tcgen05 tile: M must be a multiple of 128");
+  // (A bm=64 entry is served by a 128-row tile fed by two of the caller's 64-row
+  // boxes; when M is an odd multiple of 64 the second box of the last tile row
+  // lies past the end of A, TMA fills it with zeros and still credits its bytes,
+  // and the C map, encoded with M rows, clips the store.)
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
@@ -947,7 +973,7 @@ int oxgpu_b200_shared_free(void *ptr) {
 // the kernels receive (through the workspace tensor map and the reduction's
 // argument).
 static __device__ __align__(256) float g_static_splitk_scratch[OXGPU_STATIC_SCRATCH_BYTES / sizeof(float)];
-static float *g_static_scratch_addr[64];  // per device; filled on the first call there
+static std::atomic<float *> g_static_scratch_addr[64];  // per device; filled on the first call there
 
 int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16_t *bt, float *c, int m, int n,
                                        int k, int64_t lda, int64_t ldb, int64_t ldc, int splits,
@@ -981,17 +1007,17 @@ int oxgpu_b200_gemm_bf16_splitk_static(const uint16_t *a, const uint16_t *bt, fl
                   need, splits, m_pad, n, (unsigned)OXGPU_STATIC_SCRATCH_BYTES);
     return fail(OXGPU_E_TOO_LARGE, text);
   }
-  if (!g_static_scratch_addr[dev_index]) {
+  if (!g_static_scratch_addr[dev_index].load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (!g_static_scratch_addr[dev_index]) {
+    if (!g_static_scratch_addr[dev_index].load(std::memory_order_acquire)) {
       float *addr = nullptr;
       OX_CUDA(cudaGetSymbolAddress((void **)&addr, g_static_splitk_scratch));
       if (!addr) return fail(OXGPU_E_INVALID_ARG, "cudaGetSymbolAddress returned a null address");
-      g_static_scratch_addr[dev_index] = addr;
+      g_static_scratch_addr[dev_index].store(addr, std::memory_order_release);
     }
   }
   const unsigned flags = OXGPU_FLAG_VARIANT(OXGPU_VARIANT_SPLITK) | OXGPU_FLAG_SPLITS(splits);
-  return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, g_static_scratch_addr[dev_index],
+  return gemm_buffers(0, a, bt, c, m, n, k, lda, ldb, ldc, flags, g_static_scratch_addr[dev_index].load(std::memory_order_acquire),
                       (size_t)OXGPU_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
 }
 
@@ -1103,6 +1129,19 @@ int oxgpu_b200_release_staging(void) {
   if (s.c) OX_CUDA(cudaFree(s.c));
   s.a = s.bt = s.c = nullptr;
   s.a_bytes = s.bt_bytes = s.c_bytes = 0;
+  if (s.events) {
+    for (int i = 0; i < 64; i++) {
+      OX_CUDA(cudaEventDestroy(s.a_ready[i]));
+      OX_CUDA(cudaEventDestroy(s.c_ready[i]));
+    }
+    s.events = false;
+  }
+  if (s.in) {
+    OX_CUDA(cudaStreamDestroy(s.in));
+    OX_CUDA(cudaStreamDestroy(s.compute));
+    OX_CUDA(cudaStreamDestroy(s.out));
+    s.in = s.compute = s.out = nullptr;
+  }
   return OXGPU_OK;
 }
 

@@ -26,19 +26,10 @@ COLUMN_ALIGN = 256  # shard widths are multiples of the widest tile
 def column_partition(n: int, world: int, align: int = COLUMN_ALIGN) -> list[tuple[int, int]]:
     """Contiguous column ranges [n0, n1) per rank: widths are multiples of
     `align` except possibly the last non-empty one (the ragged tail), and block
-    counts differ by at most one."""
-    if n <= 0 or world <= 0 or align <= 0:
-        raise ValueError("n, world and align must be positive")
-    blocks = (n + align - 1) // align
-    base, extra = divmod(blocks, world)
-    out, start = [], 0
-    for r in range(world):
-        width_blocks = base + (1 if r < extra else 0)
-        n0 = min(start * align, n)
-        n1 = min((start + width_blocks) * align, n)
-        out.append((n0, n1))
-        start += width_blocks
-    return out
+    counts differ by at most one.  The rule lives in the C library
+    (oxgpu_b200_mg_column_partition), shared with the one-process driver."""
+    from .multi_gpu import column_partition as c_partition
+    return c_partition(n, world, align)
 
 
 def shard_rows_of_bt(bt_full: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -73,20 +64,34 @@ def fanout_destinations(bases: list[int], n0: int, element_bytes: int = 4) -> li
     return [b + n0 * element_bytes for b in bases]
 
 
+def host_group(group=None):
+    """A gloo group over the same ranks as `group`, for waits that must stay on
+    the host.  `group` itself when it already is gloo; otherwise a new gloo group
+    (a collective call: every rank of `group` must make it, in the same order)."""
+    if dist.get_backend(group) == "gloo":
+        return group
+    ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+    return dist.new_group(ranks=ranks, backend="gloo")
+
+
 def peers_alive(group=None, timeout_s: float = 5.0) -> bool:
     """Host-side liveness check before a launch that writes into other ranks'
     memory: True if every rank of the group reached this call within the
     time-out.  A rank that has left (between steps, nothing in flight) shows up
     here as False on the others instead of as stores into memory nobody owns.
-    Uses the process group only; no GPU work."""
+
+    `group` must be a gloo group (see host_group): the check is a monitored
+    barrier on the host with its own time-out and puts no work on any GPU.  A
+    barrier on an NCCL group would enqueue a kernel that waits on the device for
+    the absent rank, so any other backend is refused."""
     import datetime
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return True
+    if dist.get_backend(group) != "gloo":
+        raise ValueError("peers_alive needs a gloo group (sharded.host_group makes one); "
+                         "a barrier on another backend would wait on the device")
     try:
-        if dist.get_backend(group) == "gloo":
-            dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=timeout_s))
-        else:
-            dist.barrier(group=group)       # bounded by the group's own time-out
+        dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=timeout_s))
         return True
     except Exception:                        # noqa: BLE001 - any transport or time-out error means "not all here"
         return False
@@ -142,6 +147,8 @@ class FusedGatherGemm:
         if self.world > 8:
             raise ValueError("at most 8 destinations per kernel")
         self.m, self.n, self.k, self.flags = m, n, k, flags
+        # liveness checks and the completion barrier stay on the host
+        self.host_group = host_group(group) if self.world > 1 else None
         self.parts = column_partition(n, self.world)
         self.n0, self.n1 = self.parts[self.rank]
         self.width = self.n1 - self.n0
@@ -168,7 +175,7 @@ class FusedGatherGemm:
         without launching if not."""
         if tuple(bt_shard.shape) != (self.width, self.k) or tuple(a.shape) != (self.m, self.k):
             raise ValueError("operand shapes do not match this rank's shard")
-        if check_peers_s is not None and not peers_alive(self.group, check_peers_s):
+        if check_peers_s is not None and not peers_alive(self.host_group, check_peers_s):
             raise RuntimeError("a rank of the group did not answer: nothing was launched")
         if self.width == 0:
             return
@@ -178,16 +185,28 @@ class FusedGatherGemm:
     def finish(self) -> torch.Tensor:
         torch.cuda.current_stream().synchronize()
         if self.world > 1:
-            dist.barrier(group=self.group)
+            dist.barrier(group=self.host_group)
         return self.c
 
-    def close(self, barrier: bool = True) -> None:
+    def close(self, barrier: bool = True, free_own: bool = True) -> None:
         """Unmap the peers' buffers, then (after a barrier, unless a rank is
-        known to be gone) free this rank's."""
+        known to be gone) free this rank's.  free_own=False leaves this rank's
+        buffer allocated: a rank that departs while others may still have it
+        mapped must not free it (process exit releases it)."""
         for ptr in self._opened:
             self._gemm.shared_close(ptr)
         self._opened = []
         if self.world > 1 and barrier:
-            dist.barrier(group=self.group)
+            dist.barrier(group=self.host_group)
         self.c = None
-        self._buf.free()
+        if free_own:
+            self._buf.free()
+
+    def __del__(self):
+        # a dropped instance must not leak its mappings of the peers' memory
+        try:
+            for ptr in getattr(self, "_opened", []):
+                self._gemm.shared_close(ptr)
+            self._opened = []
+        except Exception:                    # noqa: BLE001 - interpreter shutdown
+            pass

@@ -29,6 +29,25 @@ from oracle import build as obuild  # noqa: E402
 from oxcamlgpu_b200 import synth  # noqa: E402
 
 
+def gpu_header_rejections(reference: str) -> list[dict]:
+    """The `.gpu` texts the reference's own tests require Gpu_metadata.parse to
+    reject: the string literals handed to `parse_fails` in test/test_frontend.ml
+    and the `malformed` literal of test/check_compiler_metadata.ml, read from the
+    reference's test sources as text and unescaped as OCaml does."""
+    import re
+    out = []
+    for rel, pattern in (("test/test_frontend.ml", r'parse_fails "((?:[^"\\]|\\.)*)";'),
+                         ("test/check_compiler_metadata.ml", r'let malformed = "((?:[^"\\]|\\.)*)" in')):
+        path = os.path.join(reference, rel)
+        for no, line in enumerate(open(path, encoding="utf-8"), 1):
+            for lit in re.findall(pattern, line):
+                text = lit.replace("\\t", "\t").replace("\\n", "\n").replace('\\"', '"')
+                out.append({"source": f"{rel}:{no}", "text": text})
+    if len(out) < 5:
+        raise SystemExit("expected at least five rejected .gpu vectors in the reference's tests")
+    return out
+
+
 def run_pin(reference: str) -> list[dict]:
     exe = obuild.build_reference_harness(reference, force=True)
     if exe is None:
@@ -111,6 +130,9 @@ def main() -> None:
     bt_bits = oracle.to_bf16(rng.standard_normal((n, k)).astype(np.float32))
     np.savez_compressed(os.path.join(HERE, "ragged_bf16_100x72x40.npz"), a_bits=a_bits,
                         bt_bits=bt_bits, expect=oracle.gemm_kmajor_bf16(a_bits, bt_bits))
+    with open(os.path.join(HERE, "gpu_header_rejected.json"), "w") as f:
+        json.dump(gpu_header_rejections(args.reference), f, indent=1)
+        f.write("\n")
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 

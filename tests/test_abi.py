@@ -61,7 +61,7 @@ def test_tmap_entry_contract_checks_need_no_device(oxlib):
     assert f(b"gemm_fast", ok_ptr, ok_ptr, ok_ptr, 256, 128, 512, None) == -4       # N % 256
     assert f(b"gemm_fast", ok_ptr, ok_ptr, ok_ptr, 256, 256, 500, None) == -4       # K % 32
     assert f(b"gemm_bf16_fast", ok_ptr, ok_ptr, ok_ptr, 256, 256, 96, None) == -4   # K % 64
-    assert f(b"gemm_bm64_bn256_s3", ok_ptr, ok_ptr, ok_ptr, 64, 256, 64, None) == -4  # served by 128-row tile
+    assert f(b"gemm_bm64_bn256_s3", ok_ptr, ok_ptr, ok_ptr, 96, 256, 64, None) == -4  # M % bm
     assert f(b"gemm_bm256_bn128_s3", ok_ptr, ok_ptr, ok_ptr, 128, 128, 64, None) == -4
 
 

@@ -1,6 +1,8 @@
 """Catalog parity with the reference's Gemm_catalog (test/gemm_catalog.ml) and
 the answers its emitter CLI is pinned to (test/check_oxcaml_signature.sh:234-251).
 Host logic only: no GPU."""
+import os
+
 import pytest
 
 from oxcamlgpu_b200 import catalog as cat
@@ -198,6 +200,18 @@ def test_gpu_header_round_trip_and_check(oxlib):
 def test_gpu_header_parse_errors(oxlib, text, msg):
     with pytest.raises(ValueError, match=msg):
         cat.parse_gpu_header(text)
+
+
+def test_gpu_header_rejects_the_reference_tests_own_vectors(oxlib, golden_dir):
+    """Every `.gpu` text the reference's tests require its parser to refuse
+    (test/test_frontend.ml:25-28, test/check_compiler_metadata.ml:8; extracted by
+    tests/golden/make_golden.py) is refused here too."""
+    import json
+    vectors = json.load(open(os.path.join(golden_dir, "gpu_header_rejected.json")))
+    assert len(vectors) >= 5
+    for v in vectors:
+        with pytest.raises(ValueError):
+            cat.parse_gpu_header(v["text"])
 
 
 def test_gpu_header_noncontiguous_args(oxlib):

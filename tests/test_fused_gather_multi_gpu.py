@@ -104,7 +104,9 @@ def _departing_worker(rank, world, port, results):
         c = fused.finish().clone()           # the shared buffer is freed by close()
         step1_ok = bool(torch.equal(c, gemm.gemm_bf16(a, bt)))
         if rank == 1:
-            fused.close(barrier=False)
+            # leave with nothing in flight: unmap the peer's buffer, but do not free this
+            # rank's own, which rank 0 may still have mapped (process exit releases it)
+            fused.close(barrier=False, free_own=False)
             results.put((rank, step1_ok, "left"))
             results.close()
             results.join_thread()

@@ -35,6 +35,53 @@ def test_column_partition(n, world):
         assert len(set(widths)) == 1 and widths[0] == n // world
 
 
+def _partition_rule(n, world, align=256):
+    """The rule stated in the header, restated here: whole `align`-column blocks,
+    counts differing by at most one, the first ranges take the extra blocks."""
+    blocks = (n + align - 1) // align
+    base, extra = divmod(blocks, world)
+    out, start = [], 0
+    for r in range(world):
+        w = base + (1 if r < extra else 0)
+        out.append((min(start * align, n), min((start + w) * align, n)))
+        start += w
+    return out
+
+
+@pytest.mark.parametrize("n,world,align", [(65536, 8, 256), (65536, 7, 256), (1000, 3, 256), (100, 8, 256),
+                                           (28672, 8, 256), (4096, 3, 128), (2 ** 31 - 1, 8, 256), (5, 5, 1)])
+def test_c_partition_function(oxlib, n, world, align):
+    """oxgpu_b200_mg_column_partition is what both the one-process driver and the
+    one-process-per-GPU wrapper use."""
+    import ctypes
+    lo, hi = (ctypes.c_int * world)(), (ctypes.c_int * world)()
+    assert oxlib.oxgpu_b200_mg_column_partition(n, world, align, lo, hi) == 0
+    assert [(lo[i], hi[i]) for i in range(world)] == _partition_rule(n, world, align)
+    assert oxlib.oxgpu_b200_mg_column_partition(0, world, align, lo, hi) == -1
+    assert oxlib.oxgpu_b200_mg_column_partition(n, world, align, None, hi) == -1
+
+
+def test_peers_alive_refuses_a_group_that_would_wait_on_the_device(monkeypatch):
+    """The liveness check must stay on the host: with any backend but gloo it
+    raises instead of issuing a barrier that would run as a kernel."""
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: 2)
+    monkeypatch.setattr(dist, "get_backend", lambda group=None: "nccl")
+    called = []
+    monkeypatch.setattr(dist, "barrier", lambda *a, **k: called.append("barrier"))
+    monkeypatch.setattr(dist, "monitored_barrier", lambda *a, **k: called.append("monitored"))
+    with pytest.raises(ValueError, match="gloo"):
+        sharded.peers_alive(timeout_s=1.0)
+    assert called == []
+    # and a non-gloo default group gets a gloo side group over the same ranks
+    made = {}
+    monkeypatch.setattr(dist, "get_process_group_ranks", lambda g: [0, 1])
+    monkeypatch.setattr(dist, "new_group", lambda ranks, backend: made.update(ranks=ranks, backend=backend) or "side")
+    assert sharded.host_group(None) == "side" and made == {"ranks": [0, 1], "backend": "gloo"}
+    monkeypatch.setattr(dist, "get_backend", lambda group=None: "gloo")
+    assert sharded.host_group("g") == "g"
+
+
 def test_partition_rejects_nonsense():
     with pytest.raises(ValueError):
         sharded.column_partition(0, 2)
@@ -147,13 +194,15 @@ def _liveness_worker(rank, world, port, results):
     import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
-    first = sharded.peers_alive(timeout_s=5.0)          # everybody is here
+    side = sharded.host_group(None)                     # gloo default group: used as it is
+    assert side is None
+    first = sharded.peers_alive(side, timeout_s=5.0)    # everybody is here
     if rank == 1:
         results.put((rank, first, None))
         results.close()
         results.join_thread()
         os._exit(0)                                     # leaves between steps
-    second = sharded.peers_alive(timeout_s=2.0)         # rank 1 is gone
+    second = sharded.peers_alive(side, timeout_s=2.0)   # rank 1 is gone
     results.put((rank, first, second))
     results.close()
     results.join_thread()
