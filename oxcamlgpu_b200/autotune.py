@@ -8,7 +8,12 @@ the buffer entry points plus the catalog entry points by name.
 
 Timing protocol as in the reference's bench (bench/bench.py:186-212): CUDA
 events, L2 flushed before every launch, median; one short cool-down before each
-candidate's window (the reference passes --cooldown 1).
+candidate's window (the reference passes --cooldown 1).  Like the reference's
+sweep, which goes through its bench and so refuses to time a kernel whose
+result is wrong (bench/bench.py:294-305), every candidate's output is checked
+once before its window -- three sampled rows against the exact kernel (the
+bit-exact restatement of the host loop) -- and a candidate that fails is
+reported and dropped, not timed.
 """
 from __future__ import annotations
 
@@ -70,9 +75,18 @@ def _median_ms(fn, slab, warmup: int, repeat: int, cooldown: float) -> float:
     return statistics.median(s.elapsed_time(e) for s, e in evs)
 
 
+def check_tolerance(element: str, k: int, a_max: float, b_max: float) -> float:
+    """1e-5 * sqrt(K) * max|A| * max|B|, inputs rounded identically on both sides;
+    5e-5 for TF32 with K >= 4096 (the matrix unit's truncating accumulator)."""
+    scale = 5e-5 if (element != "bf16" and k >= 4096) else 1e-5
+    return scale * (k ** 0.5) * a_max * b_max
+
+
 def sweep(m: int, n: int, k: int, element: str = "bf16", warmup: int = 3, repeat: int = 10,
-          cooldown: float = 1.0, seed: int = 0, std: float = 1.0):
-    """Returns (cublas_ms, [(label, ms, tflops, fraction_of_cublas)] best first)."""
+          cooldown: float = 1.0, seed: int = 0, std: float = 1.0, rejected: list | None = None):
+    """Returns (cublas_ms, [(label, ms, tflops, fraction_of_cublas)] best first).
+    Candidates whose result is outside the tolerance are appended to `rejected`
+    as (label, error, tolerance) and left out of the table."""
     dev = torch.device("cuda", torch.cuda.current_device())
     dtype = torch.bfloat16 if element == "bf16" else torch.float32
     a = torch.empty(m, k, device=dev, dtype=dtype)
@@ -91,6 +105,9 @@ def sweep(m: int, n: int, k: int, element: str = "bf16", warmup: int = 3, repeat
     run = gemm.gemm_bf16 if element == "bf16" else gemm.gemm_tf32
     flops = 2.0 * m * n * k
     cublas_ms = _median_ms(lambda: torch.matmul(a, bt.t(), out=c_ref), slab, warmup, repeat, cooldown)
+    sample = torch.tensor(sorted({0, m // 2, m - 1}), device=dev)
+    exact = gemm.gemm_exact(a[sample].contiguous(), bt, gemm.INPUT_BF16 if element == "bf16" else gemm.INPUT_TF32)
+    tol = check_tolerance(element, k, float(a.float().abs().max()), float(bt.float().abs().max()))
     rows = []
     for label, spec in candidates(m, n, k, element):
         if isinstance(spec, str):
@@ -104,6 +121,14 @@ def sweep(m: int, n: int, k: int, element: str = "bf16", warmup: int = 3, repeat
             flags = gemm.make_flags(**spec)
             fn = lambda flags=flags: run(a, bt, c, flags=flags)
         try:
+            c.fill_(float("nan"))
+            fn()
+            err = float((c[sample] - exact).abs().max())
+            if not err <= tol:     # NaN included
+                print(f"REJECTED {label}: result off by {err} (tolerance {tol}); not timed", file=sys.stderr)
+                if rejected is not None:
+                    rejected.append((label, err, tol))
+                continue
             ms = _median_ms(fn, slab, warmup, repeat, cooldown)
         except Exception as exc:  # a variant may refuse a shape; the sweep goes on
             print(f"skip {label}: {exc}", file=sys.stderr)

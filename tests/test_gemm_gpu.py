@@ -916,3 +916,35 @@ def test_launch_count_increases():
     a = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
     gemm.gemm_bf16(a, a)
     assert gemm.launch_count() == before + 1
+
+
+def test_autotune_sweep_checks_before_it_times():
+    """The sweep verifies every candidate against the exact kernel before timing
+    it (as the reference's sweep does through its bench, bench/bench.py:294-305),
+    nothing is rejected on a healthy build, and the library's own choice is
+    close to the best candidate."""
+    from oxcamlgpu_b200 import autotune
+    rejected = []
+    cublas_ms, rows = autotune.sweep(512, 768, 320, repeat=2, warmup=1, cooldown=0, rejected=rejected)
+    assert rejected == [] and cublas_ms > 0 and len(rows) >= 8
+    labels = [r[0] for r in rows]
+    assert "auto (library default)" in labels
+    best_ms = rows[0][1]
+    auto_ms = next(r[1] for r in rows if r[0] == "auto (library default)")
+    # a 6 us kernel timed twice: allow launch jitter on top of the 5 %
+    assert auto_ms <= 1.05 * best_ms + 0.004, (auto_ms, best_ms)
+    # the check itself: a candidate that produces a wrong result is dropped, not timed
+    real = gemm.gemm_bf16
+    try:
+        def broken(a, bt, c=None, flags=0, **kw):
+            out = real(a, bt, c, flags=flags, **kw)
+            if (flags & 0xFF) == gemm.V_1CTA_128x128:
+                out[0, 0] += 1000.0
+            return out
+        gemm.gemm_bf16 = broken
+        rejected = []
+        _, rows2 = autotune.sweep(512, 768, 320, repeat=1, warmup=1, cooldown=0, rejected=rejected)
+    finally:
+        gemm.gemm_bf16 = real
+    assert rejected and all("1cta_128x128" in r[0] for r in rejected)
+    assert not any(r[0].startswith("1cta_128x128") for r in rows2)
