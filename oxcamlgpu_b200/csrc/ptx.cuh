@@ -85,6 +85,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: a thread whose phase is not complete
+// may be parked by the hardware for up to `hint_ns` and is resumed when the
+// phase completes, so a long wait costs a handful of instructions instead of a
+// polling loop.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+// Named barrier over `threads` threads (a multiple of 32) that also ORs a
+// predicate: every participant gets the same answer.
+__device__ __forceinline__ bool named_barrier_or(uint32_t id, uint32_t threads, bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"((uint32_t)flag)
+      : "memory");
+  return out != 0;
+}
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");

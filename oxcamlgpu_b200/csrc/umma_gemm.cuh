@@ -125,37 +125,28 @@ struct WaitCtx {
 };
 
 // Bounded mbarrier wait.  Returns false if the budget ran out (or another
-// role of this CTA already gave up).
-// max_nap_ns > 0: sleep between polls, 32 ns doubling up to max_nap_ns.  For waits
-// that normally last most of a tile (the epilogue waiting for an accumulator):
-// eight warps per SM polling flat out cost about 1 % of SM clock under the
-// power cap; a 256 ns ceiling gives that back and delays the wake-up by less
-// than the head start the issuer gives the epilogue.
+// role of this CTA already gave up).  The waiter is parked by the hardware
+// (try_wait with a suspend-time hint) and resumed when the phase completes, so
+// a wait that lasts a whole main loop costs a few instructions per park, not a
+// polling loop; the abort flag and the budget are looked at between parks.
+constexpr uint32_t kParkNs = 4000;
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx &ctx,
-                                             uint32_t kind, uint32_t detail, uint32_t max_nap_ns = 0) {
+                                             uint32_t kind, uint32_t detail) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
-  uint32_t spins = 0;
-  uint32_t nap = 32;
   while (true) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if (max_nap_ns) {
-      __nanosleep(nap);
-      if (nap < max_nap_ns) nap <<= 1;
-    }
-    if ((++spins & 0xffu) == 0) {
-      if (*ctx.abort_flag) return false;
-      if (ptx::globaltimer_ns() - t0 > ctx.budget_ns) {
-        if (atomicCAS(&g_device_status[0], 0u, kind) == 0u) {
-          g_device_status[1] = blockIdx.x;
-          g_device_status[2] = detail;
-          g_device_status[3] = parity;
-          g_device_status[4] = kind;
-          __threadfence();
-        }
-        *ctx.abort_flag = 1;
-        return false;
+    if (ptx::mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+    if (*ctx.abort_flag) return false;
+    if (ptx::globaltimer_ns() - t0 > ctx.budget_ns) {
+      if (atomicCAS(&g_device_status[0], 0u, kind) == 0u) {
+        g_device_status[1] = blockIdx.x;
+        g_device_status[2] = detail;
+        g_device_status[3] = parity;
+        g_device_status[4] = kind;
+        __threadfence();
       }
+      *ctx.abort_flag = 1;
+      return false;
     }
   }
 }
@@ -618,13 +609,15 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         if constexpr (NI == 1) return tn * BN + j;
         else return tn * (NI * BN) + (j / B_ROWS) * (NI * B_ROWS) + mi * B_ROWS + j % B_ROWS;
       };
-      // one lane waits (the wait can last a whole main loop); the rest of the
-      // warp parks at the shuffle instead of polling the barrier
-      uint32_t got = 0;
-      if (lane == 0)
-        got = bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w, 256u) ? 1u : 0u;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) {
+      // One lane of each group of four warps waits on the accumulator's barrier
+      // (the wait can last a whole main loop); everyone else sleeps in a named
+      // hardware barrier, which issues nothing, and the barrier's OR hands all 128
+      // threads the same verdict.
+      bool failed = false;
+      if ((ew & 3) == 0 && lane == 0)
+        failed = !bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w);
+      __syncwarp();
+      if (ptx::named_barrier_or(1u + (uint32_t)group, 128u, failed)) {
         ok = false;
         break;
       }
