@@ -26,6 +26,15 @@ constexpr int kKinds = 8;     // 0 = bf16, 1 = tf32, 2 = bf16 with bf16 C, 3 / 4
 constexpr int kVariants = 12;  // index by Variant value
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<unsigned> g_sched_seq{0};  // next queue slot of the dynamic tile schedule (round robin)
+
+// OXGPU_TILE_SCHEDULE=static keeps every launch on the static walk (cluster c
+// takes tiles c, c + clusters, ...); anything else leaves the choice to the
+// library.  Read at every launch so a process can switch.
+bool static_schedule_forced() {
+  const char *e = std::getenv("OXGPU_TILE_SCHEDULE");
+  return e && std::strcmp(e, "static") == 0;
+}
 
 struct Staging {
   void *a = nullptr, *bt = nullptr, *c = nullptr;
@@ -337,6 +346,14 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     long long ctas = work < sms ? work : sms;
     cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   }
+  // Problems that keep every cluster busy for several tiles take their tiles
+  // from a queue in walk order instead of a fixed stride, so the tiles in flight
+  // stay a compact window of the walk (see TileFeed).  Split-K keeps the static
+  // walk: its work items are tied to cluster ranks or to workspace slices.
+  p.sched_slot_plus1 = 0;
+  if (p.splits == 1 && plan.cluster_splits <= 1 && work >= 2LL * cfg.gridDim.x / shape.cta_group &&
+      !static_schedule_forced())
+    p.sched_slot_plus1 = 1 + (int)(g_sched_seq.fetch_add(1, std::memory_order_relaxed) % (unsigned)kSchedSlots);
   void *args[1] = {(void *)&p};
   OX_CUDA(cudaLaunchKernelExC(&cfg, fn, args));
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -1189,6 +1206,10 @@ int oxgpu_b200_device_status(uint32_t words[8]) {
   if (host[0] != 0) {
     uint32_t zero[8] = {};
     OX_CUDA(cudaMemcpyToSymbol(g_device_status, zero, sizeof zero));
+    // a launch that gave up may have left its tile queue half used
+    void *queue = nullptr;
+    OX_CUDA(cudaGetSymbolAddress(&queue, g_tile_queue));
+    OX_CUDA(cudaMemset(queue, 0, sizeof(unsigned int) * 2 * kSchedSlots));
     char text[160];
     std::snprintf(text, sizeof text,
                   "device wait timed out: kind %u, block %u, detail %u, parity %u", host[0], host[1],

@@ -101,6 +101,33 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
   return ok != 0;
 }
 
+// Cluster-scope acquire: pairs with a release.cluster arrival from another CTA
+// of the cluster, so data that CTA wrote into this CTA's shared memory before
+// arriving is visible after the wait.
+__device__ __forceinline__ bool mbar_try_wait_parked_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+// Store into the shared memory of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 // Named barrier over `threads` threads (a multiple of 32) that also ORs a
 // predicate: every participant gets the same answer.
 __device__ __forceinline__ bool named_barrier_or(uint32_t id, uint32_t threads, bool flag) {

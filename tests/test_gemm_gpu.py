@@ -948,3 +948,38 @@ def test_autotune_sweep_checks_before_it_times():
         gemm.gemm_bf16 = real
     assert rejected and all("1cta_128x128" in r[0] for r in rejected)
     assert not any(r[0].startswith("1cta_128x128") for r in rows2)
+
+
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+def test_dynamic_tile_schedule_matches_the_static_walk(variant, monkeypatch):
+    """Problems with several tiles per cluster hand their tiles out from a queue
+    in walk order (whichever cluster is free takes the next one); which cluster
+    computes a tile does not change its value, so the result is bit-equal to the
+    static walk's.  Back-to-back launches reuse queue slots (each launch must
+    leave its slot clean), and launches on two streams at once use different
+    slots."""
+    m, n, k = 2048, 4096, 192          # 512 tiles of 128 x 128, 32 of 512 x 256: several per cluster for the small tiles
+    if variant in ("2cta_512x256", "2cta_256x512"):
+        m, n = 8192, 8192              # 512 pair tiles on 74 pairs
+    a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
+    bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(a, 31, 1.0, 0)
+    gemm.fill_normal(bt, 31, 1.0, m * k)
+    flags = gemm.make_flags(variant)
+    monkeypatch.setenv("OXGPU_TILE_SCHEDULE", "static")
+    static = gemm.gemm_bf16(a, bt, flags=flags)
+    torch.cuda.synchronize()
+    monkeypatch.delenv("OXGPU_TILE_SCHEDULE")
+    outs = [torch.full((m, n), float("nan"), device=DEV) for _ in range(4)]
+    for c in outs[:2]:
+        gemm.gemm_bf16(a, bt, c, flags=flags)          # back to back on one stream
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    gemm.gemm_bf16(a, bt, outs[2], flags=flags, stream=s1)   # and two at once
+    gemm.gemm_bf16(a, bt, outs[3], flags=flags, stream=s2)
+    torch.cuda.synchronize()
+    for c in outs:
+        assert torch.equal(c, static)
+    rows = torch.from_numpy(_sample_rows(m, 2, 5)[:3]).long().to(DEV)
+    check_bf16(a[rows].contiguous().view(torch.int16).cpu().numpy().view(np.uint16),
+               bt.view(torch.int16).cpu().numpy().view(np.uint16), static[rows])
