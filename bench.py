@@ -2,8 +2,8 @@
 """Benchmark of the dense GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload bf16_8192|tf32_4096|tf32_8192|proj_a|proj_b|proj_c|bf16_16384|cfg5|helpers]
-                    [--gather] [--no-flush] [--no-also] [--no-cfg5]
+                    [--workload bf16_8192|tf32_4096|tf32_8192|proj_a|proj_b|proj_c|bf16_16384|cfg5|helpers|profile]
+                    [--case NAME] [--gather] [--no-flush] [--no-also] [--no-cfg5]
 
 One "step" is one GEMM over one set of synthetic operands.  Default workload:
 bf16 8192^3 (A row-major, B column-major = B^T[N,K] row-major, normal(0,1),
@@ -208,7 +208,7 @@ def metric_name(workload: str) -> str:
                 workload, f"bf16 GEMM TFLOPS {workload}")
 
 
-def workload_config(workload: str, gpus: int) -> dict:
+def workload_config(workload: str, gpus: int, flush: bool = True) -> dict:
     kind, m, n, k, dist, std, seed = WORKLOADS[workload]
     if workload == "cfg5":
         shard = f"B^T and C column-sharded over {gpus} GPU(s), A replicated; strong scaling"
@@ -221,7 +221,10 @@ def workload_config(workload: str, gpus: int) -> dict:
             "per_gpu_mnk": per_gpu, "layout": "A[M,K] row-major, B column-major (B^T[N,K] K-major), C f32 row-major",
             "inputs": f"{dist}" + (f"(0,{std})" if dist == "normal" else "[-1,1)") + f" seed {seed}, counter-based generator",
             "sharding": shard,
-            "l2": "flushed before every timed step (zeroing a slab of max(2*L2,128 MiB)); operands+C also exceed L2"}
+            "l2": ("flushed before every timed step (zeroing a slab of max(2*L2,128 MiB)); operands+C also exceed L2"
+                   if flush else
+                   "not flushed: back-to-back launches after 0.5 s of the same launches (sustained clocks); "
+                   "operands+C exceed L2")}
 
 
 def tolerance(kind: str, k: int, a_max: float, b_max: float) -> float:
@@ -261,6 +264,11 @@ class Windows:
         l2 = torch.cuda.get_device_properties(dev).L2_cache_size
         self.slab = torch.empty(max(2 * l2, 128 << 20), dtype=torch.int8, device=dev)
         self.flush = (lambda: self.slab.zero_()) if flush else (lambda: None)
+        # --no-flush is the sustained protocol: back-to-back launches, and every
+        # window is preceded by half a second of the same launches, so each engine
+        # is timed at the clock the power governor settles on for it (a window that
+        # starts on a cool GPU drifts from boost to capped clocks while it is timed)
+        self.preheat_s = 0.0 if flush else 0.5
 
     def sync(self):
         self.torch.cuda.synchronize()
@@ -270,10 +278,17 @@ class Windows:
 
     def cooldown(self):
         self.torch.cuda.synchronize()
-        time.sleep(COOLDOWN_S)
+        if not self.preheat_s:
+            time.sleep(COOLDOWN_S)
 
     def timed(self, fn, steps, warmup):
         torch = self.torch
+        if self.preheat_s:
+            t0 = time.perf_counter()
+            while time.perf_counter() - t0 < self.preheat_s:
+                for _ in range(4):
+                    fn()
+                torch.cuda.synchronize()
         for _ in range(warmup):
             self.flush()
             fn()
@@ -607,13 +622,64 @@ def run_helpers(torch, gemm, dev, peaks, size=8192, repeat=10):
                       "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"], "kernels": rows}), flush=True)
 
 
+PROFILE_CASES = ("entry_bf16_fast", "out16", "affine", "fanout8", "tf32_8192", "proj_a", "proj_b", "big_dynamic",
+                 "big_static")
+
+
+def run_profile_case(torch, gemm, dev, case: str, launches: int):
+    """--workload profile --case NAME: a few plain launches of one instantiation on
+    a small problem (a few GB at most), nothing timed -- the command an `ncu`
+    capture wraps.  entry_bf16_fast: the catalog entry `gemm_bf16_fast` with the
+    reference's own maps (runs the 256 x 512 pair tile); out16: bf16 C; affine:
+    alpha, beta * C_in and a bias row; fanout8: eight local destinations per tile;
+    tf32_8192, proj_a, proj_b: the default kernel on those shapes; big_dynamic /
+    big_static: 16384 x 32768 x 8192 with the queue-driven and the fixed-stride
+    tile schedule."""
+    shapes = {"tf32_8192": WORKLOADS["tf32_8192"][1:4], "proj_a": WORKLOADS["proj_a"][1:4],
+              "proj_b": WORKLOADS["proj_b"][1:4], "big_dynamic": (16384, 32768, 8192),
+              "big_static": (16384, 32768, 8192)}
+    m, n, k = shapes.get(case, (4096, 4096, 4096))
+    kind = "tf32" if case == "tf32_8192" else "bf16"
+    a, bt = make_operands(torch, gemm, dev, kind, m, n, k, "normal" if kind == "bf16" else "uniform", 1.0, 7)
+    if case == "big_static":
+        os.environ["OXGPU_TILE_SCHEDULE"] = "static"
+    if case == "entry_bf16_fast":
+        c = torch.empty(m, n, device=dev)
+        run = lambda: gemm.run_catalog_entry("gemm_bf16_fast", a, bt, c)
+    elif case == "out16":
+        c = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        run = lambda: gemm.gemm_bf16_out16(a, bt, c)
+    elif case == "affine":
+        c = torch.empty(m, n, device=dev)
+        c_in = torch.ones(m, n, device=dev)
+        bias = torch.ones(n, device=dev)
+        run = lambda: gemm.gemm_affine(a, bt, c, alpha=2.0, beta=0.5, bias=bias, c_in=c_in)
+    elif case == "fanout8":
+        dests = [torch.empty(m, n, device=dev) for _ in range(8)]
+        run = lambda: gemm.gemm_fanout(a, bt, dests)
+    elif kind == "tf32":
+        c = torch.empty(m, n, device=dev)
+        run = lambda: gemm.gemm_tf32(a, bt, c)
+    else:
+        c = torch.empty(m, n, device=dev)
+        run = lambda: gemm.gemm_bf16(a, bt, c)
+    for _ in range(launches):
+        run()
+    if case.startswith("big_"):           # the vendor library on the same operands, for the same counters
+        torch.mm(a, bt.t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    gemm.device_status()
+    print(json.dumps({"profile_case": case, "mnk": [m, n, k], "launches": launches}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["helpers"], default="bf16_8192")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["helpers", "profile"], default="bf16_8192")
+    ap.add_argument("--case", choices=PROFILE_CASES, default="out16", help="with --workload profile")
     ap.add_argument("--variant", default="auto")
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--group-m", type=int, default=0)
@@ -626,8 +692,8 @@ def main():
     ap.add_argument("--no-flush", action="store_true", help="back-to-back launches, no L2 flush")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.workload == "helpers" and args.impl == "reference":
-        raise SystemExit("--workload helpers has no reference arm")
+    if args.workload in ("helpers", "profile") and args.impl == "reference":
+        raise SystemExit("--workload %s has no reference arm" % args.workload)
 
     if args.impl == "reference":
         return run_reference(args)
@@ -655,6 +721,8 @@ def main():
     peaks = measured_peaks()
     if args.workload == "helpers":
         return run_helpers(torch, gemm, dev, peaks)
+    if args.workload == "profile":
+        return run_profile_case(torch, gemm, dev, args.case, max(1, min(args.steps, 5)))
 
     kind, m, n_total, k, distname, std, seed = WORKLOADS[args.workload]
     if args.workload == "cfg5":
@@ -854,7 +922,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "bf16" if kind == "bf16" else "tf32", "data": "synthetic",
-            "config": dict(workload_config(args.workload, world), variant=args.variant),
+            "config": dict(workload_config(args.workload, world, not args.no_flush), variant=args.variant),
             "median_ms": median_ms, "value_at_median": flops_all / (median_ms * 1e-3) * 1e-12,
             "cublas": {"what": "torch.matmul, same operands, %s out" % ("bf16" if kind == "bf16" else "f32 (TF32 on)"),
                        "median_ms": cublas_med, "mean_ms": cublas_mean,
