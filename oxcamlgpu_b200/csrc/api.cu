@@ -735,32 +735,43 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
     return OXGPU_OK;
   };
 
-  while (a_up < na || b_up < nb) {
-    // next upload: keep the two operands' progress balanced (as fractions)
-    const bool take_a = b_up >= nb || (a_up < na && (long long)a_up * nb <= (long long)b_up * na);
-    cudaEvent_t up = s.a_ready[ev % 64];
-    if (take_a) {
-      const int r0 = a_up * a_rows, rows = m - r0 < a_rows ? m - r0 : a_rows;
-      OX_CUDA(cudaMemcpyAsync((char *)s.a + (size_t)r0 * row_bytes, (const char *)a_host + (size_t)r0 * row_bytes,
-                              (size_t)rows * row_bytes, cudaMemcpyHostToDevice, s.in));
-      OX_CUDA(cudaEventRecord(up, s.in));
-      a_up++;
-      if (b_up > 0) {  // new block row of C against every B^T block present
-        const int cols = b_up * b_rows < n ? b_up * b_rows : n;
-        if ((st = emit(r0, rows, 0, cols, up))) return st;
+  // Two passes over the same sequence of steps: first every upload is queued (with
+  // its event), then every product and download.  Queued that way the upload
+  // stream never waits for the host thread, which needs tens of microseconds per
+  // step for the tensor maps, the launch and the event calls of a product.
+  for (int pass = 0; pass < 2; pass++) {
+    a_up = b_up = ev = 0;
+    while (a_up < na || b_up < nb) {
+      // next upload: keep the two operands' progress balanced (as fractions)
+      const bool take_a = b_up >= nb || (a_up < na && (long long)a_up * nb <= (long long)b_up * na);
+      cudaEvent_t up = s.a_ready[ev % 64];
+      if (take_a) {
+        const int r0 = a_up * a_rows, rows = m - r0 < a_rows ? m - r0 : a_rows;
+        if (pass == 0) {
+          OX_CUDA(cudaMemcpyAsync((char *)s.a + (size_t)r0 * row_bytes, (const char *)a_host + (size_t)r0 * row_bytes,
+                                  (size_t)rows * row_bytes, cudaMemcpyHostToDevice, s.in));
+          OX_CUDA(cudaEventRecord(up, s.in));
+        }
+        a_up++;
+        if (pass == 1 && b_up > 0) {  // new block row of C against every B^T block present
+          const int cols = b_up * b_rows < n ? b_up * b_rows : n;
+          if ((st = emit(r0, rows, 0, cols, up))) return st;
+        }
+      } else {
+        const int c0 = b_up * b_rows, cols = n - c0 < b_rows ? n - c0 : b_rows;
+        if (pass == 0) {
+          OX_CUDA(cudaMemcpyAsync((char *)s.bt + (size_t)c0 * row_bytes, (const char *)bt_host + (size_t)c0 * row_bytes,
+                                  (size_t)cols * row_bytes, cudaMemcpyHostToDevice, s.in));
+          OX_CUDA(cudaEventRecord(up, s.in));
+        }
+        b_up++;
+        if (pass == 1 && a_up > 0) {  // new block column of C against every A block present
+          const int rows = a_up * a_rows < m ? a_up * a_rows : m;
+          if ((st = emit(0, rows, c0, cols, up))) return st;
+        }
       }
-    } else {
-      const int c0 = b_up * b_rows, cols = n - c0 < b_rows ? n - c0 : b_rows;
-      OX_CUDA(cudaMemcpyAsync((char *)s.bt + (size_t)c0 * row_bytes, (const char *)bt_host + (size_t)c0 * row_bytes,
-                              (size_t)cols * row_bytes, cudaMemcpyHostToDevice, s.in));
-      OX_CUDA(cudaEventRecord(up, s.in));
-      b_up++;
-      if (a_up > 0) {  // new block column of C against every A block present
-        const int rows = a_up * a_rows < m ? a_up * a_rows : m;
-        if ((st = emit(0, rows, c0, cols, up))) return st;
-      }
+      ev++;
     }
-    ev++;
   }
   OX_CUDA(cudaStreamSynchronize(s.out));
   OX_CUDA(cudaStreamSynchronize(s.in));

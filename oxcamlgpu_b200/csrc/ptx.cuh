@@ -128,6 +128,14 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uin
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// Named barrier, the two halves of a one-way hand-off: arrivers do not wait.
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // Named barrier over `threads` threads (a multiple of 32) that also ORs a
 // predicate: every participant gets the same answer.
 __device__ __forceinline__ bool named_barrier_or(uint32_t id, uint32_t threads, bool flag) {

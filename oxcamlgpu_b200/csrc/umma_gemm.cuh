@@ -309,34 +309,49 @@ struct CrossSliceSum {
 // The affine epilogue on one 32-column chunk of one accumulator row (held by one
 // lane): v = (alpha * acc + beta * c_in) + bias, every step rounded on its own
 // (no fused multiply-add), so a host that applies the same three operations in
-// f32 to the plain GEMM's output gets the same bits.
-__device__ __forceinline__ void affine_chunk(uint32_t (&v)[32], const GemmParams &p, int row, int col) {
+// f32 to the plain GEMM's output gets the same bits.  It comes in two halves so
+// that the C_in values of the NEXT chunk can be fetched while this chunk is
+// computed and stored: a lane reads its own row of C_in (32 rows per warp
+// instruction, a global-memory round trip of about a microsecond), and eight
+// chunks per tile with that latency exposed cost a third of the kernel's time.
+__device__ __forceinline__ void affine_fetch(float (&ci)[32], const GemmParams &p, int row, int col) {
   const bool use_c = p.beta != 0.0f && row < p.c_rows;
   const float *c_row = use_c ? p.c_in + (long long)row * p.c_in_ld : nullptr;
 #pragma unroll
   for (int j = 0; j < 8; j++) {
     const int cj = col + 4 * j;
-    float b[4] = {0.f, 0.f, 0.f, 0.f}, ci[4] = {0.f, 0.f, 0.f, 0.f};
-    if (cj + 4 <= p.c_cols) {
-      if (p.bias) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (use_c) {
+      if (cj + 4 <= p.c_cols) {
+        t = *reinterpret_cast<const float4 *>(c_row + cj);
+      } else {
+        if (cj < p.c_cols) t.x = c_row[cj];
+        if (cj + 1 < p.c_cols) t.y = c_row[cj + 1];
+        if (cj + 2 < p.c_cols) t.z = c_row[cj + 2];
+      }
+    }
+    ci[4 * j] = t.x, ci[4 * j + 1] = t.y, ci[4 * j + 2] = t.z, ci[4 * j + 3] = t.w;
+  }
+}
+
+__device__ __forceinline__ void affine_apply(uint32_t (&v)[32], const float (&ci)[32], const GemmParams &p, int col) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const int cj = col + 4 * j;
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.bias) {
+      if (cj + 4 <= p.c_cols) {
         const float4 t = __ldg(reinterpret_cast<const float4 *>(p.bias + cj));
         b[0] = t.x, b[1] = t.y, b[2] = t.z, b[3] = t.w;
+      } else {
+        for (int q = 0; q < 4; q++)
+          if (cj + q < p.c_cols) b[q] = __ldg(p.bias + cj + q);
       }
-      if (use_c) {
-        const float4 t = *reinterpret_cast<const float4 *>(c_row + cj);
-        ci[0] = t.x, ci[1] = t.y, ci[2] = t.z, ci[3] = t.w;
-      }
-    } else {
-      for (int q = 0; q < 4; q++)
-        if (cj + q < p.c_cols) {
-          if (p.bias) b[q] = __ldg(p.bias + cj + q);
-          if (use_c) ci[q] = c_row[cj + q];
-        }
     }
 #pragma unroll
     for (int q = 0; q < 4; q++) {
       const float acc = __uint_as_float(v[4 * j + q]);
-      const float r = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, acc), __fmul_rn(p.beta, ci[q])), b[q]);
+      const float r = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, acc), __fmul_rn(p.beta, ci[4 * j + q])), b[q]);
       v[4 * j + q] = __float_as_uint(r);
     }
   }
@@ -350,7 +365,7 @@ __device__ __forceinline__ void affine_chunk(uint32_t (&v)[32], const GemmParams
 // (the reference's 256-row B^T box): UMMA `ni` of a K step reads rows
 // [ni * BN/2, (ni + 1) * BN/2) of both CTAs' stages, so accumulator column j of
 // block ni is tile column (j / (BN/2)) * BN + ni * BN/2 + j % (BN/2).
-// AFFINE: the epilogue applies alpha, beta * C_in and a bias row (affine_chunk) in
+// AFFINE: the epilogue applies alpha, beta * C_in and a bias row (affine_fetch / affine_apply) in
 // f32, before the rounding to bf16 when OUT16 is set as well.
 template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1,
           bool AFFINE = false>
@@ -451,11 +466,19 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     ptx::tmem_relinquish<CTA_GROUP>();
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
   if constexpr (CTA_GROUP == 2) {
+    __syncthreads();
     // the peer's barriers must exist before anything arrives on them remotely
     ptx::cluster_arrive();
     ptx::cluster_wait();
+  } else {
+    // The producer warp needs nothing the other warps set up (its lane initialised
+    // the barriers itself, and it never touches TMEM): it arrives and goes straight
+    // to its first loads, which are then in flight while the TMEM allocation and
+    // this hand-off complete -- about a microsecond earlier, which a problem that
+    // lasts tens of microseconds notices.
+    if (warp == 0) ptx::named_barrier_arrive(3u, kThreadsPerCta);
+    else ptx::named_barrier_sync(3u, kThreadsPerCta);
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
@@ -755,7 +778,9 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is
         // in flight while chunk c goes through shared memory to the TMA store.
         uint32_t va[32], vb[32];
+        float cia[AFFINE ? 32 : 1], cib[AFFINE ? 32 : 1];  // C_in of the current / the next chunk
         ptx::tmem_ld_32x32b_x32(t_addr, va);
+        if constexpr (AFFINE) affine_fetch(cia, p, c_row + lane, chunk_col(0));
 #pragma unroll
         for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
           uint32_t(&cur)[32] = (c & 1) ? vb : va;
@@ -763,7 +788,12 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ptx::tmem_ld_wait();
           if (c + 1 < CHUNKS_PER_GROUP) ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
           else release_unit();
-          if constexpr (AFFINE) affine_chunk(cur, p, c_row + lane, chunk_col(c));
+          if constexpr (AFFINE) {
+            float(&ci_cur)[AFFINE ? 32 : 1] = (c & 1) ? cib : cia;
+            float(&ci_nxt)[AFFINE ? 32 : 1] = (c & 1) ? cia : cib;
+            if (c + 1 < CHUNKS_PER_GROUP) affine_fetch(ci_nxt, p, c_row + lane, chunk_col(c + 1));
+            affine_apply(cur, ci_cur, p, chunk_col(c));
+          }
           // the previous store must be done reading the staging buffer
           if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();
@@ -799,8 +829,11 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ptx::tmem_ld_wait();
           if (c2 + 1 == CHUNKS_PER_GROUP / 2) release_unit();
           if constexpr (AFFINE) {  // in f32, before the one rounding to bf16
-            affine_chunk(va, p, c_row + lane, chunk_col(2 * c2));
-            affine_chunk(vb, p, c_row + lane, chunk_col(2 * c2) + 32);
+            float ci[32];
+            affine_fetch(ci, p, c_row + lane, chunk_col(2 * c2));
+            affine_apply(va, ci, p, chunk_col(2 * c2));
+            affine_fetch(ci, p, c_row + lane, chunk_col(2 * c2) + 32);
+            affine_apply(vb, ci, p, chunk_col(2 * c2) + 32);
           }
           if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();

@@ -31,3 +31,33 @@ def test_reference_arm_other_ranks_do_nothing():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_reference_arm_uses_the_affinity_mask_not_omp_num_threads():
+    """torchrun sets OMP_NUM_THREADS=1 for every rank; the reference arm must
+    still use every host thread the process may run on, or its number (and any
+    ratio against it) is off by the core count."""
+    env = dict(os.environ, OMP_NUM_THREADS="1", RANK="0", WORLD_SIZE="2", LOCAL_RANK="0")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                          "--workload", "tf32_4096", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][0])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert d["n_gpus"] == 2 and d["impl"] == "reference"
+
+
+def test_bench_defaults_and_workloads():
+    """The line's extra objects are on by default and every profile case names a
+    workload the harness can build (no GPU needed to check the tables)."""
+    sys.path.insert(0, ROOT)
+    import bench
+    assert set(bench.ALSO) <= set(bench.WORKLOADS) and "cfg5" in bench.WORKLOADS
+    assert bench.WORKLOADS["cfg5"][1:4] == (32768, 65536, 8192)
+    assert bench.tolerance("bf16", 8192, 1.0, 1.0) == 1e-5 * 8192 ** 0.5
+    assert bench.tolerance("tf32", 4096, 1.0, 1.0) == 5e-5 * 4096 ** 0.5
+    assert bench.tolerance("tf32", 2048, 1.0, 1.0) == 1e-5 * 2048 ** 0.5
+    r = bench.roofline_of("bf16", 128, 8192, 8192, 0.045, bench.measured_peaks(), None)
+    assert r["bound"] == "hbm" and 0 < r["frac"] < 1
+    r = bench.roofline_of("bf16", 8192, 8192, 8192, 0.68, bench.measured_peaks(), 1.0e9)
+    assert r["bound"] == "tensor" and r["traffic"] == 1.0e9 and r["algorithmic_bytes"] == 536870912
