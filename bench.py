@@ -58,7 +58,7 @@ WORKLOADS = {
 ALSO = ("tf32_8192", "tf32_4096", "proj_a", "proj_b", "proj_c")
 # DRAM bytes (read + write) of one launch of the dominant kernel, from one ncu
 # capture of the same kernel (profiles/umma_gemm_*.md); None = not captured.
-NCU_TRAFFIC_BYTES = {"bf16_8192": 1.085e9, "tf32_4096": 0.247e9, "proj_c": 0.1406e9}
+NCU_TRAFFIC_BYTES = {"bf16_8192": 1.043e9, "tf32_4096": 0.247e9, "proj_c": 0.1406e9}
 COOLDOWN_S = 1.0   # before each engine's window (the reference uses 3 s, bench/bench.py:307-309)
 
 
@@ -281,7 +281,9 @@ class Windows:
         if not self.preheat_s:
             time.sleep(COOLDOWN_S)
 
-    def timed(self, fn, steps, warmup):
+    def timed(self, fn, steps, warmup, counter=None):
+        """Returns the per-step milliseconds; with `counter` (a function returning the
+        library's launch count) self.launches is what the timed steps alone launched."""
         torch = self.torch
         if self.preheat_s:
             t0 = time.perf_counter()
@@ -294,11 +296,13 @@ class Windows:
             fn()
         self.sync()
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        before = counter() if counter else 0
         for s, e in evs:
             self.flush()
             s.record()
             fn()
             e.record()
+        self.launches = (counter() - before) if counter else None
         self.sync()
         return [s.elapsed_time(e) for s, e in evs]
 
@@ -347,8 +351,12 @@ def cublas_same_work(torch, kind, a, bt_t, c_out):
 
 
 def measure_also(torch, gemm, win, name, peaks, steps=10, warmup=5):
-    """One extra workload on one GPU: ours, cuBLAS on the same work, ours again."""
+    """One extra workload on one GPU: ours, cuBLAS on the same work, ours again.
+    Launches shorter than a millisecond get 40 steps, so that a window is not over
+    before the clocks have settled."""
     kind, m, n, k, distname, std, seed = WORKLOADS[name]
+    if 2.0 * m * n * k < 1e12:
+        steps = max(steps, 40)
     a, bt = make_operands(torch, gemm, win.dev, kind, m, n, k, distname, std, seed)
     c = torch.empty(m, n, device=win.dev, dtype=torch.float32)
     run = (lambda: gemm.gemm_bf16(a, bt, c)) if kind == "bf16" else (lambda: gemm.gemm_tf32(a, bt, c))
@@ -752,10 +760,9 @@ def main():
     timed_steps, reduce_max = win.timed, win.reduce_max
 
     sampler = ClockSampler(local)
-    launches0 = gemm.launch_count()
     sampler.__enter__()
-    ours_ms = timed_steps(run_gemm, args.steps, args.warmup)
-    launches = gemm.launch_count() - launches0 - args.warmup
+    ours_ms = timed_steps(run_gemm, args.steps, args.warmup, counter=gemm.launch_count)
+    launches = win.launches
     total_ms = reduce_max(sum(ours_ms))
     ms_per_step = total_ms / args.steps
     median_ms = reduce_max(statistics.median(ours_ms))

@@ -306,54 +306,66 @@ struct CrossSliceSum {
   }
 };
 
-// The affine epilogue on one 32-column chunk of one accumulator row (held by one
-// lane): v = (alpha * acc + beta * c_in) + bias, every step rounded on its own
-// (no fused multiply-add), so a host that applies the same three operations in
-// f32 to the plain GEMM's output gets the same bits.  It comes in two halves so
-// that the C_in values of the NEXT chunk can be fetched while this chunk is
-// computed and stored: a lane reads its own row of C_in (32 rows per warp
-// instruction, a global-memory round trip of about a microsecond), and eight
-// chunks per tile with that latency exposed cost a third of the kernel's time.
-__device__ __forceinline__ void affine_fetch(float (&ci)[32], const GemmParams &p, int row, int col) {
-  const bool use_c = p.beta != 0.0f && row < p.c_rows;
-  const float *c_row = use_c ? p.c_in + (long long)row * p.c_in_ld : nullptr;
+// The affine epilogue: v = (alpha * acc + beta * c_in) + bias, every step rounded
+// on its own (no fused multiply-add), so a host that applies the same three
+// operations in f32 to the plain GEMM's output gets the same bits.  It is
+// applied to a 32x32 f32 sub-tile that already sits in the warp's swizzled
+// staging buffer, not to the accumulator's own register layout (lane = row):
+// there a lane would read its own row of C_in, 32 different 128-byte lines per
+// warp instruction, and the load/store unit was busy with that for a quarter of
+// a tile's time (4096^3: 151 us against 102 us plain).
+// In the staged layout a warp instruction covers 4 rows x 128 bytes (lane -> row
+// 4i + lane / 8, 16-byte piece lane % 8), so the reads of C_in are whole
+// 128-byte lines, 4 per instruction, and they are issued one chunk ahead
+// (affine_fetch_rows) so their latency hides behind the previous chunk's store.
+struct AffineRows {
+  float4 ci[8];
+};
+
+__device__ __forceinline__ void affine_fetch_rows(AffineRows &t, const GemmParams &p, int row0, int col0, int lane) {
+  const int piece_col = col0 + 4 * (lane & 7);
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
-    const int cj = col + 4 * j;
-    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (use_c) {
-      if (cj + 4 <= p.c_cols) {
-        t = *reinterpret_cast<const float4 *>(c_row + cj);
+  for (int i = 0; i < 8; i++) {
+    const int row = row0 + 4 * i + (lane >> 3);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.beta != 0.0f && row < p.c_rows) {
+      const float *src = p.c_in + (long long)row * p.c_in_ld + piece_col;
+      if (piece_col + 4 <= p.c_cols) {
+        v = *reinterpret_cast<const float4 *>(src);
       } else {
-        if (cj < p.c_cols) t.x = c_row[cj];
-        if (cj + 1 < p.c_cols) t.y = c_row[cj + 1];
-        if (cj + 2 < p.c_cols) t.z = c_row[cj + 2];
+        if (piece_col < p.c_cols) v.x = src[0];
+        if (piece_col + 1 < p.c_cols) v.y = src[1];
+        if (piece_col + 2 < p.c_cols) v.z = src[2];
       }
     }
-    ci[4 * j] = t.x, ci[4 * j + 1] = t.y, ci[4 * j + 2] = t.z, ci[4 * j + 3] = t.w;
+    t.ci[i] = v;
   }
 }
 
-__device__ __forceinline__ void affine_apply(uint32_t (&v)[32], const float (&ci)[32], const GemmParams &p, int col) {
-#pragma unroll
-  for (int j = 0; j < 8; j++) {
-    const int cj = col + 4 * j;
-    float b[4] = {0.f, 0.f, 0.f, 0.f};
-    if (p.bias) {
-      if (cj + 4 <= p.c_cols) {
-        const float4 t = __ldg(reinterpret_cast<const float4 *>(p.bias + cj));
-        b[0] = t.x, b[1] = t.y, b[2] = t.z, b[3] = t.w;
-      } else {
-        for (int q = 0; q < 4; q++)
-          if (cj + q < p.c_cols) b[q] = __ldg(p.bias + cj + q);
-      }
+__device__ __forceinline__ void affine_apply_staged(uint32_t buf, const AffineRows &t, const GemmParams &p, int col0,
+                                                    int lane) {
+  const int piece = lane & 7, piece_col = col0 + 4 * piece;
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.bias) {
+    if (piece_col + 4 <= p.c_cols) {
+      b = __ldg(reinterpret_cast<const float4 *>(p.bias + piece_col));
+    } else {
+      if (piece_col < p.c_cols) b.x = __ldg(p.bias + piece_col);
+      if (piece_col + 1 < p.c_cols) b.y = __ldg(p.bias + piece_col + 1);
+      if (piece_col + 2 < p.c_cols) b.z = __ldg(p.bias + piece_col + 2);
     }
+  }
 #pragma unroll
-    for (int q = 0; q < 4; q++) {
-      const float acc = __uint_as_float(v[4 * j + q]);
-      const float r = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, acc), __fmul_rn(p.beta, ci[4 * j + q])), b[q]);
-      v[4 * j + q] = __float_as_uint(r);
-    }
+  for (int i = 0; i < 8; i++) {
+    const int r = 4 * i + (lane >> 3);
+    const uint32_t addr = buf + (uint32_t)r * 128u + (uint32_t)((piece ^ (r & 7)) << 4);
+    float4 a = ptx::ld_shared_v4(addr);
+    const float4 c = t.ci[i];
+    a.x = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, a.x), __fmul_rn(p.beta, c.x)), b.x);
+    a.y = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, a.y), __fmul_rn(p.beta, c.y)), b.y);
+    a.z = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, a.z), __fmul_rn(p.beta, c.z)), b.z);
+    a.w = __fadd_rn(__fadd_rn(__fmul_rn(p.alpha, a.w), __fmul_rn(p.beta, c.w)), b.w);
+    ptx::st_shared_v4(addr, __float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w));
   }
 }
 
@@ -365,7 +377,7 @@ __device__ __forceinline__ void affine_apply(uint32_t (&v)[32], const float (&ci
 // (the reference's 256-row B^T box): UMMA `ni` of a K step reads rows
 // [ni * BN/2, (ni + 1) * BN/2) of both CTAs' stages, so accumulator column j of
 // block ni is tile column (j / (BN/2)) * BN + ni * BN/2 + j % (BN/2).
-// AFFINE: the epilogue applies alpha, beta * C_in and a bias row (affine_fetch / affine_apply) in
+// AFFINE: the epilogue applies alpha, beta * C_in and a bias row (affine_apply_staged) in
 // f32, before the rounding to bf16 when OUT16 is set as well.
 template <int KIND, int BM_CTA, int BN, int CTA_GROUP, bool OUT16 = false, bool FANOUT = false, int NI = 1,
           bool AFFINE = false>
@@ -778,9 +790,9 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         // Software-pipelined over 32-column chunks: the TMEM load of chunk c+1 is
         // in flight while chunk c goes through shared memory to the TMA store.
         uint32_t va[32], vb[32];
-        float cia[AFFINE ? 32 : 1], cib[AFFINE ? 32 : 1];  // C_in of the current / the next chunk
+        AffineRows cin_a, cin_b;  // C_in of the current / the next chunk (AFFINE only)
         ptx::tmem_ld_32x32b_x32(t_addr, va);
-        if constexpr (AFFINE) affine_fetch(cia, p, c_row + lane, chunk_col(0));
+        if constexpr (AFFINE) affine_fetch_rows(cin_a, p, c_row, chunk_col(0), lane);
 #pragma unroll
         for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
           uint32_t(&cur)[32] = (c & 1) ? vb : va;
@@ -789,10 +801,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           if (c + 1 < CHUNKS_PER_GROUP) ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)((c + 1) * 32), nxt);
           else release_unit();
           if constexpr (AFFINE) {
-            float(&ci_cur)[AFFINE ? 32 : 1] = (c & 1) ? cib : cia;
-            float(&ci_nxt)[AFFINE ? 32 : 1] = (c & 1) ? cia : cib;
-            if (c + 1 < CHUNKS_PER_GROUP) affine_fetch(ci_nxt, p, c_row + lane, chunk_col(c + 1));
-            affine_apply(cur, ci_cur, p, chunk_col(c));
+            if (c + 1 < CHUNKS_PER_GROUP) affine_fetch_rows((c & 1) ? cin_a : cin_b, p, c_row, chunk_col(c + 1), lane);
           }
           // the previous store must be done reading the staging buffer
           if (lane == 0) ptx::tma_store_wait_read<0>();
@@ -803,6 +812,10 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           for (int j = 0; j < 8; j++) {
             ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
                               cur[4 * j + 2], cur[4 * j + 3]);
+          }
+          if constexpr (AFFINE) {
+            __syncwarp();  // the whole sub-tile is staged: transform it in place, four rows per instruction
+            affine_apply_staged(buf, (c & 1) ? cin_b : cin_a, p, chunk_col(c), lane);
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
@@ -826,17 +839,38 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           uint32_t va[32], vb[32];
           ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c2 * 64), va);
           ptx::tmem_ld_32x32b_x32(t_addr + (uint32_t)(c2 * 64 + 32), vb);
+          AffineRows cin_a, cin_b;
+          if constexpr (AFFINE) {  // in flight while the accumulator chunks arrive
+            affine_fetch_rows(cin_a, p, c_row, chunk_col(2 * c2), lane);
+            affine_fetch_rows(cin_b, p, c_row, chunk_col(2 * c2) + 32, lane);
+          }
           ptx::tmem_ld_wait();
           if (c2 + 1 == CHUNKS_PER_GROUP / 2) release_unit();
-          if constexpr (AFFINE) {  // in f32, before the one rounding to bf16
-            float ci[32];
-            affine_fetch(ci, p, c_row + lane, chunk_col(2 * c2));
-            affine_apply(va, ci, p, chunk_col(2 * c2));
-            affine_fetch(ci, p, c_row + lane, chunk_col(2 * c2) + 32);
-            affine_apply(vb, ci, p, chunk_col(2 * c2) + 32);
-          }
           if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();
+          if constexpr (AFFINE) {
+            // In f32, before the one rounding to bf16: each 32-column half goes through
+            // the staging buffer as f32, is transformed there four rows per instruction
+            // (coalesced C_in, see affine_apply_staged) and comes back to its row's lane.
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              uint32_t(&v)[32] = h == 0 ? va : vb;
+#pragma unroll
+              for (int j = 0; j < 8; j++)
+                ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                                  v[4 * j + 3]);
+              __syncwarp();
+              affine_apply_staged(buf, h == 0 ? cin_a : cin_b, p, chunk_col(2 * c2) + 32 * h, lane);
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 t = ptx::ld_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4));
+                v[4 * j] = __float_as_uint(t.x), v[4 * j + 1] = __float_as_uint(t.y);
+                v[4 * j + 2] = __float_as_uint(t.z), v[4 * j + 3] = __float_as_uint(t.w);
+              }
+              __syncwarp();
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 8; j++) {
             uint32_t(&src)[32] = j < 4 ? va : vb;
