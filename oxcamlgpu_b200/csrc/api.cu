@@ -345,15 +345,7 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
     cfg.gridDim = dim3((unsigned)work, 1, 1);
-    // Two slices of a 128-column tile exchange halves by pushing them (see the
-    // kernel); every other slicing parks and pulls.  OXGPU_CLUSTER_REDUCE=pull
-    // keeps the pull form everywhere (same bits either way).
-    const char *form = std::getenv("OXGPU_CLUSTER_REDUCE");
-    const bool pull_only = form && std::strcmp(form, "pull") == 0;
-    p.cluster_reduce = (plan.cluster_splits == 2 && plan.variant == VARIANT_1CTA_128x128 && !plan.fanout &&
-                        !plan.affine && !plan.out16 && !pull_only)
-                           ? 2
-                           : 1;
+    p.cluster_reduce = 1;
   } else {
     const int sms = dev.sm_count;
     long long ctas = work < sms ? work : sms;

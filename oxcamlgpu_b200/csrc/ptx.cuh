@@ -128,16 +128,6 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uin
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
-// 16 bytes from registers into the shared memory of a CTA of this cluster
-// (address from map_to_cta), completing as 16 transaction bytes on an mbarrier
-// of that CTA: the receiver waits on its own barrier, no cluster-wide barrier.
-__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
-                                            uint32_t cluster_bar) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
-               ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar)
-               : "memory");
-}
-
 // Named barrier, the two halves of a one-way hand-off: arrivers do not wait.
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -60,7 +60,6 @@ enum WaitKind : uint32_t {
   WAIT_DRAIN = 5,       // teardown waiting for in-flight work
   WAIT_SELFTEST = 6,    // the bounded-wait self test
   WAIT_TILE = 7,        // a role waiting for the producer to announce the next tile
-  WAIT_PEER_HALF = 8,   // cluster split-K: waiting for the other CTA's half of the partial tile
 };
 
 struct GemmParams {
@@ -89,11 +88,6 @@ struct GemmParams {
   // partial tiles in their own shared memory, and each CTA then sums one column
   // range of the tile across the cluster through distributed shared memory and
   // writes it to C.  No workspace, no second kernel, fixed summation order.
-  // 1: every CTA parks its partial tile and pulls its column range from the
-  // others after a cluster barrier (2, 4 or 8 slices).  2: two slices of a
-  // 128-column tile -- each CTA pushes the half the other one owns straight from
-  // registers into the owner's shared memory (st.async onto the owner's
-  // mbarrier) and adds what it receives to its own half, still in registers.
   int cluster_reduce;
   float *c_ptr;
   long long c_ld;
@@ -413,8 +407,6 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   static_assert(BM_CTA == 128 || BM_CTA == 256, "unsupported tile");
   static_assert(NI == 1 || (NI == 2 && MI == 1 && CTA_GROUP == 2 && !OUT16), "unsupported column blocking");
   static_assert(CHUNKS_PER_GROUP >= 1 && CHUNKS % 2 == 0, "unsupported tile width");
-  // the instantiation that can run the push form of the in-cluster split-K reduction
-  constexpr bool kPushReduce = CTA_GROUP == 1 && MI == 1 && BN == 128 && !OUT16 && !FANOUT && !AFFINE;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -433,8 +425,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   const uint32_t abort_slot = tmem_slot + 4u;
   const uint32_t ring_bar = abort_slot + 4u;
   const uint32_t ring_tile = ring_bar + 8u * kTileRing;
-  const uint32_t reduce_bar = ring_tile + 4u * kTileRing;  // cluster split-K, push form: the peer's half has landed
-  static_assert(16 * kMaxStages + 32 + 32 + 8 + 4 + 4 + 12 * kTileRing + 8 <= kBarrierRegionBytes, "barrier region");
+  static_assert(16 * kMaxStages + 32 + 32 + 8 + 4 + 4 + 12 * kTileRing <= kBarrierRegionBytes, "barrier region");
   uint8_t *const generic_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   volatile uint32_t *const tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t *>(generic_base + (tmem_slot - smem_base));
@@ -471,13 +462,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     }
     ptx::mbar_init(drain_bar, 1);
     for (int i = 0; i < kTileRing; i++) ptx::mbar_init(ring_bar + 8u * i, 1);
-    ptx::mbar_init(reduce_bar, 1);
     ptx::fence_mbar_init();
-    if constexpr (kPushReduce) {
-      // push form of the cluster reduction: this CTA will receive half a partial
-      // tile (128 rows x 64 columns of f32) from its peer
-      if (p.cluster_reduce == 2) ptx::mbar_arrive_expect_tx(reduce_bar, 128u * 64u * 4u);
-    }
   }
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(map_a);
@@ -504,21 +489,11 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     // to its first loads, which are then in flight while the TMEM allocation and
     // this hand-off complete -- about a microsecond earlier, which a problem that
     // lasts tens of microseconds notices.
-    // Push form of the cluster reduction: the peer's barrier must exist before this
-    // CTA stores into the peer's shared memory at the end of its main loop.  Every
-    // thread arrives here and waits where it has nothing else to do (the issuer and
-    // the epilogue warps before their first wait, the producer warp after its last
-    // load), so the cluster barrier costs nothing on the way in.
-    if constexpr (kPushReduce) {
-      if (p.cluster_reduce == 2) ptx::cluster_arrive();
-    }
     if (warp == 0) ptx::named_barrier_arrive(3u, kThreadsPerCta);
     else ptx::named_barrier_sync(3u, kThreadsPerCta);
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  bool push_reduce = false;
-  if constexpr (kPushReduce) push_reduce = p.cluster_reduce == 2;
 
   // ---- roles ------------------------------------------------------------------
   if (warp == 0) {
@@ -605,10 +580,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
         }
       }
     }
-    if (push_reduce) ptx::cluster_wait();
   } else if (warp == 1) {
     // ===== UMMA issuer (examples/kernels/gemm.ml:107-141, the K loop) =====
-    if (push_reduce) ptx::cluster_wait();
     if (lane == 0 && is_leader) {
       int stage = 0;
       uint32_t phase = 0;
@@ -738,7 +711,6 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     }
   } else {
     // ===== epilogue (examples/kernels/gemm.ml:143-161) =====
-    if (push_reduce) ptx::cluster_wait();
     const int quad = warp & 3;         // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     const int ew = warp - 2;           // 0..7, staging slot
     const int group = ew >> 2;         // 0 or 1
@@ -784,65 +756,6 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       ptx::tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                               (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
-      if constexpr (kPushReduce) {
-        if (push_reduce) {
-          // Two K slices of one 128 x 128 tile in the two CTAs of the cluster; CTA r
-          // owns columns [64 r, 64 r + 64), which are exactly what epilogue group r
-          // holds.  The group holding the PEER's columns sends them, straight from
-          // registers, into the peer's staging area (idle in this mode; row r at
-          // 256 r bytes, 16-byte pieces XOR-swizzled by r % 16), each store counting
-          // 16 bytes on the peer's barrier.  The group holding this CTA's own columns
-          // waits for the peer's 32 KiB, adds them (slice 0 + slice 1; f32 addition
-          // commutes, so both CTAs produce the bits of the ascending-slice sum) and
-          // writes C.  No cluster barrier, no parked copy of the own half.
-          const uint32_t rank = ptx::cluster_ctarank();
-          const int row = quad * 32 + lane;
-          const uint32_t row_base = staging_base + (uint32_t)row * 256u;
-          uint32_t v0[32], v1[32];
-          ptx::tmem_ld_32x32b_x32(t_addr, v0);
-          ptx::tmem_ld_32x32b_x32(t_addr + 32u, v1);
-          ptx::tmem_ld_wait();
-          if ((uint32_t)group != rank) {
-            const uint32_t peer_row = ptx::map_to_cta(row_base, rank ^ 1u);
-            const uint32_t peer_bar = ptx::map_to_cta(reduce_bar, rank ^ 1u);
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-              uint32_t(&v)[32] = j < 8 ? v0 : v1;
-              const int o = 4 * (j & 7);
-              ptx::st_async_v4(peer_row + (uint32_t)((j ^ (lane & 15)) << 4), v[o], v[o + 1], v[o + 2], v[o + 3],
-                               peer_bar);
-            }
-          } else {
-            if (bounded_wait<true>(reduce_bar, 0u, wctx, WAIT_PEER_HALF, (uint32_t)w)) {
-              const int g_row = tm * 128 + row;
-              const int g_col0 = tn * BN + group * 64;
-              float *c_line = p.c_ptr + (long long)g_row * p.c_ld + g_col0;
-#pragma unroll
-              for (int j = 0; j < 16; j++) {
-                uint32_t(&v)[32] = j < 8 ? v0 : v1;
-                const int o = 4 * (j & 7);
-                const float4 in = ptx::ld_shared_v4(row_base + (uint32_t)((j ^ (lane & 15)) << 4));
-                float4 out;
-                out.x = __uint_as_float(v[o]) + in.x;
-                out.y = __uint_as_float(v[o + 1]) + in.y;
-                out.z = __uint_as_float(v[o + 2]) + in.z;
-                out.w = __uint_as_float(v[o + 3]) + in.w;
-                const int col = g_col0 + 4 * j;
-                if (g_row < p.c_rows) {
-                  if (col + 4 <= p.c_cols) {
-                    *reinterpret_cast<float4 *>(c_line + 4 * j) = out;
-                  } else {
-                    const float e[4] = {out.x, out.y, out.z, out.w};
-                    for (int q = 0; q < 4; q++)
-                      if (col + q < p.c_cols) c_line[4 * j + q] = e[q];
-                  }
-                }
-              }
-            }
-          }
-          continue;  // exactly one work item per CTA in this mode
-        }
-      }
       if constexpr (CTA_GROUP == 1 && MI == 1) {
         if (p.cluster_reduce) {
           // Leave this CTA's partial tile in its own shared memory, in the (now
@@ -981,7 +894,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
 
   // ---- split-K reduction across the cluster --------------------------------------
   if constexpr (CTA_GROUP == 1 && MI == 1) {
-    if (p.cluster_reduce && !push_reduce) {
+    if (p.cluster_reduce) {
       // Every thread of every CTA passes both cluster barriers, whatever
       // happened in its role (a timed-out wait included), so nobody is left
       // waiting; the data is only meaningful if no wait timed out, which the

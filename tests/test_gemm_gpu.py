@@ -376,34 +376,6 @@ def test_cluster_split_k(variant, splits, m, n, k):
         assert torch.equal(c.contiguous(), ws)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 8192, 8192), (100, 520, 1000), (384, 1024, 4096), (128, 128, 128)])
-def test_cluster_split_k_push_form_matches_the_pull_form(m, n, k, monkeypatch):
-    """Two slices of a 128-column tile exchange halves by pushing them from
-    registers into the owner's shared memory (no cluster barrier, no parked copy
-    of the own half); every other slicing parks and pulls.  Same slices, same
-    two-term sum: bit-equal, for bf16 and TF32, ragged edges included, and on
-    back-to-back launches (the receiving barrier starts fresh every launch)."""
-    rng = np.random.default_rng(k + n)
-    a_bits, bt_bits = rand_bf16(rng, m, k, 0.02), rand_bf16(rng, n, k, 0.02)
-    a, bt = bf16_tensor(a_bits), bf16_tensor(bt_bits)
-    flags = gemm.make_flags("cluster_splitk_128x128", splits=2)
-    monkeypatch.setenv("OXGPU_CLUSTER_REDUCE", "pull")
-    pull = gemm.gemm_bf16(a, bt, flags=flags)
-    pull32 = gemm.gemm_tf32(a.float(), bt.float(), flags=flags)
-    torch.cuda.synchronize()
-    monkeypatch.delenv("OXGPU_CLUSTER_REDUCE")
-    pad = torch.full((m + 2, n + 8), float("nan"), device=DEV)
-    c = pad[1:m + 1, 4:n + 4]
-    for _ in range(3):
-        c.fill_(float("nan"))
-        gemm.gemm_bf16(a, bt, c, flags=flags)
-        assert torch.equal(c, pull)
-    assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
-    assert torch.isnan(pad[:, :4]).all() and torch.isnan(pad[:, n + 4:]).all()
-    assert torch.equal(gemm.gemm_tf32(a.float(), bt.float(), flags=flags), pull32)
-    check_bf16(a_bits, bt_bits, c.contiguous())
-
-
 def test_skinny_problem_takes_the_cluster_split_k_path_by_default():
     a = torch.empty(128, 8192, device=DEV, dtype=torch.bfloat16)
     bt = torch.empty(8192, 8192, device=DEV, dtype=torch.bfloat16)
