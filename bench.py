@@ -135,6 +135,26 @@ class ClockSampler:
                 "power_w_max": round(top, 1), "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def nvlink_rx_bytes(devices):
+    """Bytes each device has received over NVLink so far (payload, all links
+    summed), read through NVML's field queries -- counters only, nothing is set.
+    None when the driver does not expose them."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        out = []
+        for d in devices:
+            h = pynvml.nvmlDeviceGetHandleByIndex(d)
+            # scope id 0xffffffff = the sum over the device's links; the value is in KiB
+            v = pynvml.nvmlDeviceGetFieldValues(h, [(pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX, 0xFFFFFFFF)])[0]
+            if v.nvmlReturn != 0:
+                return None
+            out.append(int(v.value.ullVal) * 1024)
+        return out
+    except Exception:
+        return None
+
+
 def cpu_sample(kind: str, m: int, n: int, k: int, dist: str, std: float, seed: int, target_s: float,
                threads: int | None = None):
     """Prepare a bounded sample of the workload for the oracle (the C restatement
@@ -522,7 +542,15 @@ def measure_cfg5(torch, gemm, ngpu: int, flags: int, peaks: dict, do_gather: boo
                         f.zero_()
                     for _ in range(2):
                         step(gather=mode, c_full=full)
+                    rx0 = nvlink_rx_bytes(devices)
                     gruns = [step(gather=mode, c_full=full) for _ in range(5)]
+                    rx1 = nvlink_rx_bytes(devices)
+                    if rx0 and rx1:
+                        # NVLink payload bytes into each GPU per step, from the driver's counters,
+                        # beside the (g-1)/g of C that must arrive
+                        per_step = [(b - a0) / 5.0 for a0, b in zip(rx0, rx1)]
+                        gat[mode + "_nvlink_rx_bytes_per_gpu_per_step"] = {"min": min(per_step), "max": max(per_step),
+                                                                           "expected": recv}
                     ok = all(bool(torch.equal(f[rows.to(f.device)].cpu(), mine)) for f in full)
                     if not ok:
                         raise SystemExit(f"replicated C ({mode}) disagrees with the shards")
@@ -879,6 +907,25 @@ def main():
                "pcie_gbs_duplex_slowest_rank": {"h2d": up_gbs, "d2h": down_gbs},
                "bound_ms": bound_ms, "frac_of_bound": bound_ms / (sec / e2e_steps * 1e3),
                "bound": "max(H2D bytes / H2D rate, D2H bytes / D2H rate), both directions busy, all ranks at once"}
+        if kind == "bf16":
+            # the same call with bf16 C: half the bytes come back, the upload alone bounds it
+            c16_buf = multi_gpu.PinnedHostBuffer(m * n * 2, local)
+            c16_h = c16_buf.tensor((m, n), torch.bfloat16)
+            for _ in range(2):
+                gemm.gemm_bf16_out16_host(a_h, bt_h, c16_h, flags)
+            win.sync()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                gemm.gemm_bf16_out16_host(a_h, bt_h, c16_h, flags)
+            sec16 = reduce_max(time.perf_counter() - t0)
+            ok16 = float((c16_h[rows.cpu()].float() - exact.cpu()).abs().max()) <= tol + float(exact.abs().max()) * 2.0 ** -8
+            if not ok16:
+                raise SystemExit("host-buffer path with bf16 C disagrees with the exact kernel")
+            e2e["bf16_out"] = {"api": "oxgpu_b200_gemm_bf16_out16_host", "ms_per_step": sec16 / e2e_steps * 1e3,
+                               "value": flops_all / (sec16 / e2e_steps) * 1e-12, "d2h_bytes_per_step": m * n * 2,
+                               "bound_ms": max(h2d / (up_gbs * 1e9), m * n * 2 / (down_gbs * 1e9)) * 1e3}
+            del c16_h
+            c16_buf.free()
         del a_h, bt_h, c_h
         for b in bufs:
             b.free()

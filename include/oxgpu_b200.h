@@ -486,6 +486,11 @@ OXGPU_API int oxgpu_b200_gemm_bf16_host(const uint16_t *a_host, const uint16_t *
                                         float *c_host, int m, int n, int k, unsigned flags);
 OXGPU_API int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *c_host,
                                         int m, int n, int k, unsigned flags);
+/* The same with bf16 C (one rounding to nearest even at the store, as
+ * oxgpu_b200_gemm_bf16_out16): half the bytes come back over PCIe, so the call is
+ * bound by the upload alone.  N % 8 == 0. */
+OXGPU_API int oxgpu_b200_gemm_bf16_out16_host(const uint16_t *a_host, const uint16_t *bt_host,
+                                              uint16_t *c_host, int m, int n, int k, unsigned flags);
 OXGPU_API int oxgpu_b200_release_staging(void);
 
 /* ---- synthetic operands -------------------------------------------------- */

@@ -139,3 +139,10 @@ external mg_gemm_bf16_host :
   (int, Bigarray.int16_unsigned_elt, Bigarray.c_layout) Bigarray.Array2.t ->
   (float, Bigarray.float32_elt, Bigarray.c_layout) Bigarray.Array2.t -> int -> int -> unit
   = "oxgpu_ml_mg_gemm_bf16_host_byte" "oxgpu_ml_mg_gemm_bf16_host"
+
+(* Host operands, bf16 C (bits as uint16): half the bytes come back over PCIe. *)
+external gemm_bf16_out16_host :
+  (int, Bigarray.int16_unsigned_elt, Bigarray.c_layout) Bigarray.Array2.t ->
+  (int, Bigarray.int16_unsigned_elt, Bigarray.c_layout) Bigarray.Array2.t ->
+  (int, Bigarray.int16_unsigned_elt, Bigarray.c_layout) Bigarray.Array2.t -> int -> unit
+  = "oxgpu_ml_gemm_bf16_out16_host"

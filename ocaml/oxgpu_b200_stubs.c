@@ -415,3 +415,21 @@ CAMLprim value oxgpu_ml_mg_gemm_bf16_host_byte(value *argv, int argn) {
   (void)argn;
   return oxgpu_ml_mg_gemm_bf16_host(argv[0], argv[1], argv[2], argv[3], argv[4], argv[5]);
 }
+
+/* bf16 C on the host (bits as uint16): half the bytes come back over PCIe. */
+CAMLprim value oxgpu_ml_gemm_bf16_out16_host(value a, value bt, value c, value flags) {
+  CAMLparam4(a, bt, c, flags);
+  int m = (int)Caml_ba_array_val(a)->dim[0], k = (int)Caml_ba_array_val(a)->dim[1];
+  int n = (int)Caml_ba_array_val(bt)->dim[0];
+  if (Caml_ba_array_val(bt)->dim[1] != k || Caml_ba_array_val(c)->dim[0] != m ||
+      Caml_ba_array_val(c)->dim[1] != n)
+    caml_invalid_argument("gemm_bf16_out16_host: expected A[M,K], B^T[N,K], C[M,N]");
+  const uint16_t *pa = Caml_ba_data_val(a), *pb = Caml_ba_data_val(bt);
+  uint16_t *pc = Caml_ba_data_val(c);
+  unsigned f = (unsigned)Int_val(flags);
+  caml_release_runtime_system();
+  int st = oxgpu_b200_gemm_bf16_out16_host(pa, pb, pc, m, n, k, f);
+  caml_acquire_runtime_system();
+  check(st);
+  CAMLreturn(Val_unit);
+}

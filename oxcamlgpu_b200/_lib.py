@@ -127,6 +127,8 @@ def lib() -> ctypes.CDLL:
                                        ctypes.c_uint], c_int),
         "oxgpu_b200_gemm_tf32_host": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                        ctypes.c_uint], c_int),
+        "oxgpu_b200_gemm_bf16_out16_host": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             ctypes.c_uint], c_int),
         "oxgpu_b200_release_staging": ([], c_int),
         "oxgpu_b200_fill_uniform": ([c_void_p, sz, c_int, u32, u64, c_void_p], c_int),
         "oxgpu_b200_fill_normal": ([c_void_p, sz, c_int, u32, ctypes.c_float, u64, c_void_p], c_int),

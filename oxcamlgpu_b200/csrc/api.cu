@@ -673,28 +673,32 @@ int ensure_staging(Staging &s, size_t a_bytes, size_t bt_bytes, size_t c_bytes) 
 // blocks already present, or a new block column against the A blocks already
 // present) and starts its download.  Uploads, GEMMs and downloads run on three
 // streams chained by events.
-int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, int m, int n, int k,
-              unsigned flags) {
+int gemm_host(int kind, const void *a_host, const void *bt_host, void *c_host, int m, int n, int k,
+              unsigned flags, bool out16 = false) {
   const int esize = kind == 0 ? 2 : 4;
+  const size_t csize = out16 ? 2 : 4;  // bytes per element of C
   if (!a_host || !bt_host || !c_host) return fail(OXGPU_E_INVALID_ARG, "null host pointer");
   if (m <= 0 || n <= 0 || k <= 0) return fail(OXGPU_E_INVALID_ARG, "M, N and K must be positive");
   if (((int64_t)k * esize) % 16 || n % 4)
     return fail(OXGPU_E_SHAPE, "rows of A/B^T must be multiples of 16 bytes and N a multiple of 4");
+  if (out16 && n % 8) return fail(OXGPU_E_SHAPE, "bf16 C needs N to be a multiple of 8");
   int dev_index, st;
   DeviceState *dev = nullptr;
   if ((st = current_device(&dev_index, &dev))) return st;
   Staging &s = dev->staging;
   std::lock_guard<std::mutex> lock(g_staging_mutex);
   const size_t a_bytes = (size_t)m * k * esize, bt_bytes = (size_t)n * k * esize;
-  const size_t c_bytes = (size_t)m * n * sizeof(float);
+  const size_t c_bytes = (size_t)m * n * csize;
   if ((st = ensure_staging(s, a_bytes, bt_bytes, c_bytes))) return st;
 
-  // Row blocks: multiples of 256 rows, about 16 per operand (at most 16).  The
+  // Row blocks: multiples of 256 rows, about 6 per operand (at most 16).  The
   // part of C that can be computed grows with the square of the fraction of the
-  // operands that has landed, so the download trails the upload by design; small
-  // blocks keep what is still to be computed and sent after the last upload small.
+  // operands that has landed, so the download trails the upload by design; smaller
+  // blocks shorten what is left to compute and send after the last upload, but
+  // every copy costs a start-up gap on its stream (8192^3, blocks per operand ->
+  // ms: 3 -> 7.43, 4 -> 7.19, 6 -> 6.99, 8 -> 7.28, 12 -> 7.19, 16 -> 7.63).
   auto block_rows_of = [](int rows) {
-    int b = ((rows / 16 + 255) / 256) * 256;
+    int b = ((rows / 6 + 255) / 256) * 256;
     if (b < 256) b = 256;
     while ((rows + b - 1) / b > 16) b *= 2;
     return b;
@@ -723,15 +727,16 @@ int gemm_host(int kind, const void *a_host, const void *bt_host, float *c_host, 
     OX_CUDA(cudaStreamWaitEvent(s.compute, ready, 0));
     const char *a_dev = (const char *)s.a + (size_t)r0 * row_bytes;
     const char *b_dev = (const char *)s.bt + (size_t)c0 * row_bytes;
-    float *c_dev = (float *)s.c + (size_t)r0 * n + c0;
-    int st2 = gemm_buffers(kind, a_dev, b_dev, c_dev, rows, cols, k, k, k, n, flags, nullptr, 0, s.compute);
+    char *c_dev = (char *)s.c + ((size_t)r0 * n + c0) * csize;
+    int st2 = gemm_buffers(kind, a_dev, b_dev, (float *)c_dev, rows, cols, k, k, k, n, flags, nullptr, 0, s.compute,
+                           out16);
     if (st2) return st2;
     cudaEvent_t done = s.c_ready[ev % 64];
     OX_CUDA(cudaEventRecord(done, s.compute));
     OX_CUDA(cudaStreamWaitEvent(s.out, done, 0));
-    OX_CUDA(cudaMemcpy2DAsync(c_host + (size_t)r0 * n + c0, (size_t)n * sizeof(float), c_dev,
-                              (size_t)n * sizeof(float), (size_t)cols * sizeof(float), (size_t)rows,
-                              cudaMemcpyDeviceToHost, s.out));
+    OX_CUDA(cudaMemcpy2DAsync((char *)c_host + ((size_t)r0 * n + c0) * csize, (size_t)n * csize, c_dev,
+                              (size_t)n * csize, (size_t)cols * csize, (size_t)rows, cudaMemcpyDeviceToHost,
+                              s.out));
     return OXGPU_OK;
   };
 
@@ -1151,6 +1156,15 @@ int oxgpu_b200_gemm_bf16_host(const uint16_t *a_host, const uint16_t *bt_host, f
 int oxgpu_b200_gemm_tf32_host(const float *a_host, const float *bt_host, float *c_host, int m, int n,
                               int k, unsigned flags) {
   return gemm_host(1, a_host, bt_host, c_host, m, n, k, flags);
+}
+
+int oxgpu_b200_gemm_bf16_out16_host(const uint16_t *a_host, const uint16_t *bt_host, uint16_t *c_host, int m,
+                                    int n, int k, unsigned flags) {
+  unsigned v = flags & 0xffu;
+  if (v == VARIANT_1CTA_256x128 || v == VARIANT_2CTA_256x128 || v == VARIANT_SPLITK ||
+      v == VARIANT_CLUSTER_SPLITK_128x256 || v == VARIANT_CLUSTER_SPLITK_128x128)
+    return fail(OXGPU_E_INVALID_ARG, "this variant has no bf16-output kernel");
+  return gemm_host(0, a_host, bt_host, c_host, m, n, k, flags, true);
 }
 
 int oxgpu_b200_release_staging(void) {

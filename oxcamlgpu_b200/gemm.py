@@ -373,6 +373,20 @@ def gemm_bf16_host(a_host: torch.Tensor, bt_host: torch.Tensor, c_host: torch.Te
     return c_host
 
 
+def gemm_bf16_out16_host(a_host: torch.Tensor, bt_host: torch.Tensor, c_host: torch.Tensor,
+                         flags: int = 0) -> torch.Tensor:
+    """Host-buffer entry point with bf16 C: half the bytes come back over PCIe."""
+    if a_host.is_cuda or bt_host.is_cuda or c_host.is_cuda:
+        raise ValueError("host entry point takes CPU tensors")
+    if c_host.dtype != torch.bfloat16:
+        raise ValueError("C must be a bf16 CPU tensor")
+    m, k = a_host.shape
+    n = bt_host.shape[0]
+    check(lib().oxgpu_b200_gemm_bf16_out16_host(a_host.data_ptr(), bt_host.data_ptr(), c_host.data_ptr(),
+                                                m, n, k, flags))
+    return c_host
+
+
 def gemm_tf32_host(a_host: torch.Tensor, bt_host: torch.Tensor, c_host: torch.Tensor, flags: int = 0) -> torch.Tensor:
     if a_host.is_cuda or bt_host.is_cuda or c_host.is_cuda:
         raise ValueError("host entry point takes CPU tensors")

@@ -488,6 +488,16 @@ def test_host_buffer_entry_point():
     for _ in range(2):
         gemm.gemm_bf16_host(a_h, b_h, c_h)
         check_bf16(a_bits, bt_bits, c_h)
+    # bf16 C on the host: equal to the device-side bf16-output GEMM of the same blocks' tiles
+    # up to the tile choice, and within the bound after one rounding to bf16
+    c16 = torch.zeros((m, n), dtype=torch.bfloat16).pin_memory()
+    gemm.gemm_bf16_out16_host(a_h, b_h, c16)
+    expect16 = oracle.gemm_kmajor_bf16(a_bits, bt_bits, threads=oracle.max_threads())
+    tol16 = strict_tol(k, float(np.abs(oracle.of_bf16(a_bits)).max()), float(np.abs(oracle.of_bf16(bt_bits)).max()))
+    got16 = c16.float().numpy()
+    assert (np.abs(got16 - expect16) <= tol16 + np.abs(expect16) * 2.0 ** -8).all()   # one rounding to bf16
+    with pytest.raises(OxgpuError):
+        gemm.gemm_bf16_out16_host(a_h, b_h[:, :].contiguous()[:516], torch.zeros((m, 516), dtype=torch.bfloat16))
     a32 = rng.uniform(-1, 1, (300, 64)).astype(np.float32)
     b32 = rng.uniform(-1, 1, (260, 64)).astype(np.float32)
     c32 = torch.empty(300, 260)
