@@ -372,11 +372,11 @@ def cublas_same_work(torch, kind, a, bt_t, c_out):
 
 def measure_also(torch, gemm, win, name, peaks, steps=10, warmup=5):
     """One extra workload on one GPU: ours, cuBLAS on the same work, ours again.
-    Launches shorter than a millisecond get 40 steps, so that a window is not over
-    before the clocks have settled."""
+    Launches shorter than a millisecond get 40 steps after 100 warm-up steps, so
+    that a window is neither over nor begun before the clocks have settled."""
     kind, m, n, k, distname, std, seed = WORKLOADS[name]
     if 2.0 * m * n * k < 1e12:
-        steps = max(steps, 40)
+        steps, warmup = max(steps, 40), max(warmup, 100)   # (both engines; 100 flushed steps are 10-25 ms)
     a, bt = make_operands(torch, gemm, win.dev, kind, m, n, k, distname, std, seed)
     c = torch.empty(m, n, device=win.dev, dtype=torch.float32)
     run = (lambda: gemm.gemm_bf16(a, bt, c)) if kind == "bf16" else (lambda: gemm.gemm_tf32(a, bt, c))

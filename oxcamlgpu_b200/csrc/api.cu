@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -301,6 +302,22 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   const double operand_bytes = ((double)m * k + (double)n * k) * (plan.kind == 0 ? 2 : 4);
   p.hint_a = p.hint_b = operand_bytes <= 768.0 * 1024 * 1024 ? 2 : 0;
   p.hint_c = 1;
+  // An operand whose every row feeds one or two tiles only (B^T when M is a tile
+  // row or two, A when N is) is streamed, not reused: its loads are marked
+  // evict-first, so they recycle their own lines instead of pushing out the other
+  // operand -- or whatever dirty lines L2 holds, whose write-back would then share
+  // HBM with the stream -- and the operand that every tile re-reads is kept with
+  // evict-last.  With L2 full of dirty lines (the bench's flush), 128 x 8192 x 8192:
+  // 43.0 -> 36.9 us (the vendor library: 36.9), 128 x 28672 x 8192: 112.7 -> 104.4
+  // (106.6), 128 x 8192 x 28672: 104.4 -> 94.3 (92.3).
+  const int rows_of_tiles = (m + shape.tile_m - 1) / shape.tile_m, cols_of_tiles = (n + shape.tile_n - 1) / shape.tile_n;
+  if (rows_of_tiles <= 2 && cols_of_tiles > 2) {
+    p.hint_a = 2;
+    p.hint_b = 1;
+  } else if (cols_of_tiles <= 2 && rows_of_tiles > 2) {
+    p.hint_a = 1;
+    p.hint_b = 2;
+  }
   p.wait_budget_ns = wait_budget_ns();
 
   std::atomic<bool> &attr = dev.attr_set[attr_kind][plan.variant];
@@ -382,38 +399,79 @@ int check_buffers(const void *a, const void *bt, const float *c, int m, int n, i
   return OXGPU_OK;
 }
 
+// Slices of the in-cluster split-K when the caller leaves the choice to the
+// library: as many as fill the GPU once, a power of two, at most 8, each at least
+// 32 K blocks long (the reduction at the end costs microseconds whatever the
+// slice length: 128 x 4096 x 4096 takes 22.6 us with 2 slices of 32 K blocks,
+// 32.8 us with 8 slices of 8).
+int auto_cluster_slices(int sm_count, long long tiles, int num_kb) {
+  int s = 8;
+  while (s > 1 && (tiles * s > sm_count || num_kb / s < 32)) s >>= 1;
+  return s;
+}
+
 // Variant choice for the buffer entry points.  Large problems take the CTA-pair
-// 256x256 tile (least shared-memory and L2 traffic per flop); problems with few
-// tiles fall back to smaller tiles so more SMs have work.
-int choose_variant(const DeviceState &dev, int m, int n, int k) {
-  (void)k;
+// 512x256 tile (least shared-memory and L2 traffic per flop).  Everything smaller
+// is decided by an estimate of each candidate's time in SM clocks: waves of
+// tiles x K blocks x clocks per K block, where a K block costs a CTA the larger
+// of its tensor time and the time to take its operand bytes from L2 (about 45
+// bytes per clock per SM, which is what the kernels sustain), never less than
+// the problem's bytes at the HBM rate, plus the reduction tail of a split.  The
+// tall pair tiles need M to fill at least three quarters of them (with M = 128 a
+// 512-row pair tile would do four times the work: 174 us instead of 111 us at
+// 128 x 28672 x 8192).  What the estimate changed against a fixed cascade
+// (measured, L2 flushed, us): 384 x 8192 x 8192 88 -> one wave of 256x256 pair
+// tiles; 256 x 8192 x 8192 50 -> 256x128 pair tiles; 2048^3 32 -> 256x256.
+int choose_variant(const DeviceState &dev, int m, int n, int k, int kbe, int esize) {
   auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
-  const int pairs = dev.sm_count / 2;
+  const int sms = dev.sm_count, pairs = sms / 2;
+  auto fills = [&](int tm) { return 4LL * m >= 3LL * (long long)((m + tm - 1) / tm) * tm; };
   // The 512x256 pair tile moves a quarter less operand data per flop than
   // 256x256 (48 instead of 64 bytes per clock per SM at full tensor rate), which
   // is what limits the kernel at boost clocks: 95 % against 91.5 % of cuBLAS at
   // bf16 8192^3, even though it cannot double-buffer its accumulator.
-  // (A tile taller than the problem is mostly padding: with M = 128 a 512-row
-  // pair tile would do four times the work, 174 us instead of 111 us at
-  // 128 x 28672 x 8192.  Tall tiles need M to fill at least three quarters of them.)
-  auto fills = [&](int tm) { return 4LL * m >= 3LL * (long long)((m + tm - 1) / tm) * tm; };
   if (fills(512) && tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
-  if (fills(256) && tiles(256, 256) >= pairs) return VARIANT_2CTA_256x256;
-  if (fills(256) && tiles(256, 128) >= pairs) return VARIANT_2CTA_256x128;
-  // Fewer tiles than SMs: these problems stream one operand from HBM and the
-  // time is set by the busiest SM's bytes.  A full wave of one-CTA tiles first
-  // (128-column tiles stream B^T faster than 256-column ones when M is a single
-  // tile row) ...
-  if (tiles(128, 256) >= dev.sm_count) return VARIANT_1CTA_128x256;
-  if (tiles(128, 128) >= dev.sm_count) return VARIANT_1CTA_128x128;
-  // ... otherwise, when K is long, split it across a cluster so every SM has work.
-  // 128-column tiles with few, long slices: the reduction at the end costs
-  // microseconds, so a slice should be at least 32 K blocks (128 x 4096 x 4096:
-  // 22.6 us with 2 slices of 32 against 32.8 us with 8 slices of 8; 128 x 8192 x
-  // 8192: 41.0 us with 128-column tiles x 2 against 43.0 us with 256 x 4).
-  if (k >= 2048 && tiles(128, 128) * 2 <= dev.sm_count) return VARIANT_CLUSTER_SPLITK_128x128;
-  if (tiles(128, 256) >= dev.sm_count / 2) return VARIANT_1CTA_128x256;
-  return VARIANT_1CTA_128x128;
+
+  const int num_kb = (k + kbe - 1) / kbe;
+  const double bytes_per_clk = 45.0;    // what one SM takes from L2
+  const double hbm_bytes_per_clk = 3282.0;  // 6.45 TB/s at 1.965 GHz, all SMs together
+  const double floor_clk = (((double)m + n) * k * esize + (double)m * n * 4.0) / hbm_bytes_per_clk;
+  struct Candidate {
+    int variant, tile_m, tile_n, ctas_per_tile;
+    double stage_bytes, tensor_clk, wave_clk;  // per K block and CTA; fixed cost per wave of tiles
+    bool cluster_split;
+  };
+  const Candidate candidates[] = {
+      {VARIANT_2CTA_512x256, 512, 256, 2, 49152, 1024, 3000, false},
+      {VARIANT_2CTA_256x256, 256, 256, 2, 32768, 512, 1000, false},
+      {VARIANT_2CTA_256x128, 256, 128, 2, 24576, 256, 1000, false},
+      {VARIANT_1CTA_128x256, 128, 256, 1, 49152, 512, 1000, false},
+      {VARIANT_1CTA_128x128, 128, 128, 1, 32768, 256, 1000, false},
+      {VARIANT_CLUSTER_SPLITK_128x128, 128, 128, 1, 32768, 256, 1000, true},
+      {VARIANT_CLUSTER_SPLITK_128x256, 128, 256, 1, 49152, 512, 1000, true},
+  };
+  int best = VARIANT_1CTA_128x128;
+  double best_clk = 0;
+  for (const Candidate &c : candidates) {
+    if (c.tile_m > 128 && !fills(c.tile_m)) continue;
+    const long long t = tiles(c.tile_m, c.tile_n);
+    const double kb_clk = std::max(c.stage_bytes / bytes_per_clk, c.tensor_clk);
+    double clk;
+    if (c.cluster_split) {
+      const int s = auto_cluster_slices(sms, t, num_kb);
+      if (s < 2 || k < 2048) continue;
+      clk = std::max((double)((num_kb + s - 1) / s) * kb_clk + c.wave_clk, floor_clk) + 5000.0 * s;
+    } else {
+      const long long units = sms / c.ctas_per_tile;
+      const long long waves = (t + units - 1) / units;
+      clk = std::max((double)waves * (num_kb * kb_clk + c.wave_clk), floor_clk);
+    }
+    if (best_clk == 0 || clk < best_clk) {
+      best_clk = clk;
+      best = c.variant;
+    }
+  }
+  return best;
 }
 
 int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n, int k, int64_t lda,
@@ -434,7 +492,7 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   const bool splitk = variant == VARIANT_SPLITK;
   const bool was_auto = variant == VARIANT_AUTO;
   if (was_auto) {
-    variant = choose_variant(*dev, m, n, k);
+    variant = choose_variant(*dev, m, n, k, kind == 0 ? 64 : 32, esize);
     if (out16 && (variant == VARIANT_CLUSTER_SPLITK_128x256 || variant == VARIANT_CLUSTER_SPLITK_128x128))
       variant = VARIANT_1CTA_128x128;  // the cluster reduction writes f32 only
   }
@@ -447,10 +505,7 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
     const int num_kb = (k + (kind == 0 ? 64 : 32) - 1) / (kind == 0 ? 64 : 32);
     const long long tiles = (long long)((m + 127) / 128) * ((n + tile_n - 1) / tile_n);
     int s = splits;
-    if (s <= 0) {  // as many slices as fill the GPU once, a power of two, at most 8, each at least 32 K blocks
-      s = 8;
-      while (s > 1 && (tiles * s > dev->sm_count || num_kb / s < 32)) s >>= 1;
-    }
+    if (s <= 0) s = auto_cluster_slices(dev->sm_count, tiles, num_kb);
     while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) s >>= 1;  // every slice gets a K block
     if (s != 1 && s != 2 && s != 4 && s != 8)
       return fail(OXGPU_E_INVALID_ARG, "cluster split-K takes 2, 4 or 8 slices");
