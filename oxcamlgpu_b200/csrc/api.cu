@@ -399,11 +399,9 @@ int check_buffers(const void *a, const void *bt, const float *c, int m, int n, i
   return OXGPU_OK;
 }
 
-// Slices of the in-cluster split-K when the caller leaves the choice to the
-// library: as many as fill the GPU once, a power of two, at most 8, each at least
-// 32 K blocks long (the reduction at the end costs microseconds whatever the
-// slice length: 128 x 4096 x 4096 takes 22.6 us with 2 slices of 32 K blocks,
-// 32.8 us with 8 slices of 8).
+// Slices of the in-cluster split-K when the caller names the variant but not
+// the slice count: as many as fill the GPU once, a power of two, at most 8, each
+// at least 32 K blocks long.
 int auto_cluster_slices(int sm_count, long long tiles, int num_kb) {
   int s = 8;
   while (s > 1 && (tiles * s > sm_count || num_kb / s < 32)) s >>= 1;
@@ -412,20 +410,24 @@ int auto_cluster_slices(int sm_count, long long tiles, int num_kb) {
 
 // Variant choice for the buffer entry points.  Large problems take the CTA-pair
 // 512x256 tile (least shared-memory and L2 traffic per flop).  Everything smaller
-// is decided by an estimate of each candidate's time in SM clocks: waves of
-// tiles x K blocks x clocks per K block, where a K block costs a CTA the larger
-// of its tensor time and the time to take its operand bytes from L2 (about 45
-// bytes per clock per SM, which is what the kernels sustain), never less than
-// the problem's bytes at the HBM rate, plus the reduction tail of a split.  The
+// is decided by an estimate of each candidate's time in SM clocks at boost:
+// waves of tiles x (K blocks x clocks per K block + a fixed cost per tile), never
+// less than the problem's bytes at the HBM rate, plus the reduction tail of an
+// in-cluster split.  The clocks per K block are measured ones (one wave of each
+// tile at K = 8192, L2 flushed): what a CTA sustains is set by how fast it takes
+// its operand bytes from L2, 40-70 bytes per clock depending on the tile.  The
 // tall pair tiles need M to fill at least three quarters of them (with M = 128 a
 // 512-row pair tile would do four times the work: 174 us instead of 111 us at
 // 128 x 28672 x 8192).  What the estimate changed against a fixed cascade
-// (measured, L2 flushed, us): 384 x 8192 x 8192 88 -> one wave of 256x256 pair
-// tiles; 256 x 8192 x 8192 50 -> 256x128 pair tiles; 2048^3 32 -> 256x256.
-int choose_variant(const DeviceState &dev, int m, int n, int k, int kbe, int esize) {
+// (measured, L2 flushed, us): 384 x 8192 x 8192 88 -> 55 (one wave of 256x256
+// pair tiles), 512 x 8192 x 8192 88 -> 55, 2048^3 32 -> 25, 256 x 8192 x 8192
+// 50 -> 47 (128x256 tiles, two slices), 128 x 4096 x 4096 23.5 -> 21.4 (four
+// slices).
+int choose_variant(const DeviceState &dev, int m, int n, int k, int kbe, int esize, int *cluster_slices) {
   auto tiles = [&](int tm, int tn) { return (long long)((m + tm - 1) / tm) * ((n + tn - 1) / tn); };
   const int sms = dev.sm_count, pairs = sms / 2;
   auto fills = [&](int tm) { return 4LL * m >= 3LL * (long long)((m + tm - 1) / tm) * tm; };
+  *cluster_slices = 0;
   // The 512x256 pair tile moves a quarter less operand data per flop than
   // 256x256 (48 instead of 64 bytes per clock per SM at full tensor rate), which
   // is what limits the kernel at boost clocks: 95 % against 91.5 % of cuBLAS at
@@ -433,42 +435,43 @@ int choose_variant(const DeviceState &dev, int m, int n, int k, int kbe, int esi
   if (fills(512) && tiles(512, 256) >= pairs) return VARIANT_2CTA_512x256;
 
   const int num_kb = (k + kbe - 1) / kbe;
-  const double bytes_per_clk = 45.0;    // what one SM takes from L2
   const double hbm_bytes_per_clk = 3282.0;  // 6.45 TB/s at 1.965 GHz, all SMs together
   const double floor_clk = (((double)m + n) * k * esize + (double)m * n * 4.0) / hbm_bytes_per_clk;
+  const double tile_clk = 8000.0;           // fill latency + accumulator drain of one tile
+  const double slice_tail_clk = 3000.0;     // per slice of an in-cluster split: barrier + cross-CTA sum
   struct Candidate {
     int variant, tile_m, tile_n, ctas_per_tile;
-    double stage_bytes, tensor_clk, wave_clk;  // per K block and CTA; fixed cost per wave of tiles
+    double kb_clk;  // clocks per K block of one tile
     bool cluster_split;
   };
   const Candidate candidates[] = {
-      {VARIANT_2CTA_512x256, 512, 256, 2, 49152, 1024, 3000, false},
-      {VARIANT_2CTA_256x256, 256, 256, 2, 32768, 512, 1000, false},
-      {VARIANT_2CTA_256x128, 256, 128, 2, 24576, 256, 1000, false},
-      {VARIANT_1CTA_128x256, 128, 256, 1, 49152, 512, 1000, false},
-      {VARIANT_1CTA_128x128, 128, 128, 1, 32768, 256, 1000, false},
-      {VARIANT_CLUSTER_SPLITK_128x128, 128, 128, 1, 32768, 256, 1000, true},
-      {VARIANT_CLUSTER_SPLITK_128x256, 128, 256, 1, 49152, 512, 1000, true},
+      {VARIANT_2CTA_512x256, 512, 256, 2, 1340, false}, {VARIANT_2CTA_256x256, 256, 256, 2, 700, false},
+      {VARIANT_2CTA_256x128, 256, 128, 2, 620, false},  {VARIANT_1CTA_128x256, 128, 256, 1, 820, false},
+      {VARIANT_1CTA_128x128, 128, 128, 1, 600, false},  {VARIANT_CLUSTER_SPLITK_128x128, 128, 128, 1, 600, true},
+      {VARIANT_CLUSTER_SPLITK_128x256, 128, 256, 1, 820, true},
   };
   int best = VARIANT_1CTA_128x128;
   double best_clk = 0;
+  auto consider = [&](int variant, double clk, int slices) {
+    if (best_clk == 0 || clk < best_clk) {
+      best_clk = clk;
+      best = variant;
+      *cluster_slices = slices;
+    }
+  };
   for (const Candidate &c : candidates) {
     if (c.tile_m > 128 && !fills(c.tile_m)) continue;
     const long long t = tiles(c.tile_m, c.tile_n);
-    const double kb_clk = std::max(c.stage_bytes / bytes_per_clk, c.tensor_clk);
-    double clk;
     if (c.cluster_split) {
-      const int s = auto_cluster_slices(sms, t, num_kb);
-      if (s < 2 || k < 2048) continue;
-      clk = std::max((double)((num_kb + s - 1) / s) * kb_clk + c.wave_clk, floor_clk) + 5000.0 * s;
+      if (k < 2048) continue;
+      for (int s = 2; s <= 8; s *= 2) {  // one wave, every slice at least 16 K blocks
+        if (t * s > sms || num_kb / s < 16) break;
+        consider(c.variant, std::max((double)((num_kb + s - 1) / s) * c.kb_clk + tile_clk, floor_clk) + slice_tail_clk * s, s);
+      }
     } else {
       const long long units = sms / c.ctas_per_tile;
       const long long waves = (t + units - 1) / units;
-      clk = std::max((double)waves * (num_kb * kb_clk + c.wave_clk), floor_clk);
-    }
-    if (best_clk == 0 || clk < best_clk) {
-      best_clk = clk;
-      best = c.variant;
+      consider(c.variant, std::max((double)waves * (num_kb * c.kb_clk + tile_clk), floor_clk), 0);
     }
   }
   return best;
@@ -492,7 +495,9 @@ int gemm_buffers(int kind, const void *a, const void *bt, float *c, int m, int n
   const bool splitk = variant == VARIANT_SPLITK;
   const bool was_auto = variant == VARIANT_AUTO;
   if (was_auto) {
-    variant = choose_variant(*dev, m, n, k, kind == 0 ? 64 : 32, esize);
+    int model_slices = 0;
+    variant = choose_variant(*dev, m, n, k, kind == 0 ? 64 : 32, esize, &model_slices);
+    if (model_slices > 0 && splits <= 0) splits = model_slices;
     if (out16 && (variant == VARIANT_CLUSTER_SPLITK_128x256 || variant == VARIANT_CLUSTER_SPLITK_128x128))
       variant = VARIANT_1CTA_128x128;  // the cluster reduction writes f32 only
   }
