@@ -138,21 +138,30 @@ class ClockSampler:
 def nvlink_rx_bytes(devices):
     """Bytes each device has received over NVLink so far (payload, all links
     summed), read through NVML's field queries -- counters only, nothing is set.
-    None when the driver does not expose them."""
+    Returns (list, None), or (None, reason) when the driver does not expose them."""
     try:
         import pynvml
         pynvml.nvmlInit()
+        fid = pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX      # value in KiB
         out = []
         for d in devices:
             h = pynvml.nvmlDeviceGetHandleByIndex(d)
-            # scope id 0xffffffff = the sum over the device's links; the value is in KiB
-            v = pynvml.nvmlDeviceGetFieldValues(h, [(pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX, 0xFFFFFFFF)])[0]
-            if v.nvmlReturn != 0:
-                return None
-            out.append(int(v.value.ullVal) * 1024)
-        return out
-    except Exception:
-        return None
+            v = pynvml.nvmlDeviceGetFieldValues(h, [(fid, 0xFFFFFFFF)])[0]   # scope: all links of the device
+            if v.nvmlReturn == 0:
+                out.append(int(v.value.ullVal) * 1024)
+                continue
+            total, seen = 0, 0
+            for link in range(18):                                           # else link by link
+                w = pynvml.nvmlDeviceGetFieldValues(h, [(fid, link)])[0]
+                if w.nvmlReturn == 0:
+                    total += int(w.value.ullVal) * 1024
+                    seen += 1
+            if not seen:
+                return None, "NVML returned %d for the NVLink throughput field" % v.nvmlReturn
+            out.append(total)
+        return out, None
+    except Exception as exc:                                                 # noqa: BLE001 - optional evidence
+        return None, "%s: %s" % (type(exc).__name__, exc)
 
 
 def cpu_sample(kind: str, m: int, n: int, k: int, dist: str, std: float, seed: int, target_s: float,
@@ -542,9 +551,11 @@ def measure_cfg5(torch, gemm, ngpu: int, flags: int, peaks: dict, do_gather: boo
                         f.zero_()
                     for _ in range(2):
                         step(gather=mode, c_full=full)
-                    rx0 = nvlink_rx_bytes(devices)
+                    rx0, why = nvlink_rx_bytes(devices)
                     gruns = [step(gather=mode, c_full=full) for _ in range(5)]
-                    rx1 = nvlink_rx_bytes(devices)
+                    rx1, why1 = nvlink_rx_bytes(devices)
+                    if not (rx0 and rx1):
+                        gat["nvlink_counters"] = "unavailable (%s)" % (why or why1)
                     if rx0 and rx1:
                         # NVLink payload bytes into each GPU per step, from the driver's counters,
                         # beside the (g-1)/g of C that must arrive

@@ -876,9 +876,11 @@ def test_launches_can_be_captured_in_a_cuda_graph():
     """After one eager call (attributes, occupancy query), the buffer entry
     points only encode maps on the host and launch: a loop of them captures into
     a CUDA graph, and replays give the eager result.  Covers a CTA-pair kernel, the
-    in-cluster split-K and the affine epilogue."""
+    in-cluster split-K, the affine epilogue, and a problem large enough for the
+    queue-driven tile schedule (the queue slot is part of the captured launch; every
+    replay must find it clean, i.e. the previous replay's last cluster reset it)."""
     cases = []
-    for (m, n, k) in [(1024, 5120, 256), (128, 1024, 2048)]:
+    for (m, n, k) in [(1024, 5120, 256), (128, 1024, 2048), (4096, 8192, 256)]:
         a = torch.empty(m, k, device=DEV, dtype=torch.bfloat16)
         bt = torch.empty(n, k, device=DEV, dtype=torch.bfloat16)
         gemm.fill_normal(a, 40, 0.5, 0)
