@@ -487,6 +487,18 @@ int oxgpu_b200_mg_gemm_bf16(oxgpu_mg *mg, const uint16_t *const *a_repl, const u
       return fail(OXGPU_E_INVALID_ARG, "null c_shard pointer");
     if (gather_c != OXGPU_MG_GATHER_NONE && !c_full[d]) return fail(OXGPU_E_INVALID_ARG, "null c_full pointer");
   }
+  // Everything a single device's launch would refuse is refused here, for all
+  // devices, before anything is enqueued: a device that dropped out of a
+  // collective after the others had entered it would leave them waiting.
+  if (k % 8) return fail(OXGPU_E_SHAPE, "K must be a multiple of 8 (rows of 16 bytes)");
+  auto misaligned = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+  for (int d = 0; d < mg->n; d++) {
+    if (job.n1[d] <= job.n0[d]) continue;
+    if (misaligned(a_repl[d]) || misaligned(bt_shard[d]) || (c_shard && misaligned(c_shard[d])) ||
+        (c_full && misaligned(c_full[d])))
+      return fail(OXGPU_E_ALIGN, "operand pointers must be 16-byte aligned");
+    if ((job.n1[d] - job.n0[d]) % 4) return fail(OXGPU_E_SHAPE, "shard widths must be multiples of 4 columns");
+  }
   if (gather_c == OXGPU_MG_GATHER_FUSED) {
     if (n % 4) return fail(OXGPU_E_SHAPE, "the fused gather needs N to be a multiple of 4");
     if (mg->n > 1 && !mg->peers)
