@@ -37,6 +37,21 @@ bool static_schedule_forced() {
   return e && std::strcmp(e, "static") == 0;
 }
 
+// OXGPU_DEPENDENT_LAUNCH=0 launches the GEMM kernels as ordinary stream-ordered
+// kernels; anything else lets each one start its set-up (barriers, TMEM
+// allocation, descriptor prefetch) under the tail of the kernel before it.
+bool dependent_launch_enabled() {
+  const char *e = std::getenv("OXGPU_DEPENDENT_LAUNCH");
+  return !(e && std::strcmp(e, "0") == 0);
+}
+
+// OXGPU_CLUSTER_REDUCE=dsmem keeps the two-slice in-cluster split-K on the
+// distributed-shared-memory reduction that four and eight slices use.
+bool cluster_reduce_through_dsmem() {
+  const char *e = std::getenv("OXGPU_CLUSTER_REDUCE");
+  return e && std::strcmp(e, "dsmem") == 0;
+}
+
 struct Staging {
   void *a = nullptr, *bt = nullptr, *c = nullptr;
   size_t a_bytes = 0, bt_bytes = 0, c_bytes = 0;
@@ -333,14 +348,22 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   cfg.blockDim = dim3(kThreadsPerCta, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
+  // attrs[0]: the kernel may start while the kernel before it in the stream is
+  // still running (its set-up touches no global memory and it waits for that
+  // kernel before anything else); attrs[1]: the cluster shape, when there is one.
+  cudaLaunchAttribute attrs[2];
+  const unsigned base_attrs = dependent_launch_enabled() ? 1u : 0u;
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute *const cluster_attr = attrs + base_attrs;
+  cfg.attrs = attrs;
+  cfg.numAttrs = base_attrs;
   if (shape.cta_group == 2) {
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = 2;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cluster_attr->id = cudaLaunchAttributeClusterDimension;
+    cluster_attr->val.clusterDim.x = 2;
+    cluster_attr->val.clusterDim.y = 1;
+    cluster_attr->val.clusterDim.z = 1;
+    cfg.numAttrs = base_attrs + 1;
     std::atomic<int> &cached = dev.max_clusters[attr_kind][plan.variant];
     int maxc = cached.load(std::memory_order_relaxed);
     if (maxc == 0) {
@@ -355,14 +378,18 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
   } else if (plan.cluster_splits > 1) {
     // one work item per CTA: cluster c = tile c, CTA rank = K slice
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = (unsigned)plan.cluster_splits;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cluster_attr->id = cudaLaunchAttributeClusterDimension;
+    cluster_attr->val.clusterDim.x = (unsigned)plan.cluster_splits;
+    cluster_attr->val.clusterDim.y = 1;
+    cluster_attr->val.clusterDim.z = 1;
+    cfg.numAttrs = base_attrs + 1;
     cfg.gridDim = dim3((unsigned)work, 1, 1);
-    p.cluster_reduce = 1;
+    // Two slices: the tile of C is zeroed during the main loop and both CTAs add
+    // their partial tiles to it with TMA reductions (C then stays in L2 between the
+    // zeroing and the additions, so it is not marked evict-first).  More slices: the
+    // partial tiles are summed in a fixed order through distributed shared memory.
+    p.cluster_reduce = plan.cluster_splits == 2 && !cluster_reduce_through_dsmem() ? 2 : 1;
+    if (p.cluster_reduce == 2) p.hint_c = 0;
   } else {
     const int sms = dev.sm_count;
     long long ctas = work < sms ? work : sms;

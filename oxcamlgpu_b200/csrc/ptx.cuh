@@ -151,6 +151,16 @@ __device__ __forceinline__ bool named_barrier_or(uint32_t id, uint32_t threads, 
   return out != 0;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it in the stream is still running.  `wait`
+// blocks until that kernel has completed and its writes are visible (a no-op
+// for an ordinary launch); everything before it must touch no global memory
+// that the earlier kernel may write.  `launch_dependents` lets the kernel after
+// this one start its own set-up the same way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
@@ -218,6 +228,16 @@ __device__ __forceinline__ void tma_store_2d_hint(const void *map, int c0, int c
       : "memory");
 }
 
+// 2-D tile reduction shared -> global: every f32 of the box is added to the
+// element of the tensor it maps to (the addition is done at the L2, so boxes from
+// different CTAs may target the same elements).  Same bulk-group completion as a
+// store.
+__device__ __forceinline__ void tma_reduce_add_2d(const void *map, int c0, int c1, uint32_t smem_src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"((uint64_t)map), "r"(c0), "r"(c1), "r"(smem_src)
+               : "memory");
+}
+
 // 2-D tile store shared -> global through the bulk-group mechanism.
 __device__ __forceinline__ void tma_store_2d(const void *map, int c0, int c1, uint32_t smem_src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
@@ -235,6 +255,15 @@ __device__ __forceinline__ void tma_store_wait_read() {
 template <int N>
 __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Order this thread's ordinary global-memory writes before later accesses to the
+// same memory through the async proxy (TMA stores and reductions), its own or --
+// after a release/acquire hand-over -- another thread's.
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+__device__ __forceinline__ void st_global_v4_zero(float *dst) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %1, %1, %1};" ::"l"(dst), "r"(0u) : "memory");
 }
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA).
 __device__ __forceinline__ void fence_proxy_async_smem() {

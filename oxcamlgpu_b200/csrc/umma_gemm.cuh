@@ -88,6 +88,11 @@ struct GemmParams {
   // partial tiles in their own shared memory, and each CTA then sums one column
   // range of the tile across the cluster through distributed shared memory and
   // writes it to C.  No workspace, no second kernel, fixed summation order.
+  // (cluster_reduce == 1.)  With two slices there is a shorter way, cluster_reduce
+  // == 2: the tile of C is zeroed while the main loop runs, and each CTA then adds
+  // its partial tile to it with TMA reductions (the L2 does the additions; with two
+  // addends the order cannot change the sum).  The epilogue is then the ordinary
+  // one -- no parking, no cross-CTA reads, no cluster barrier on the way out.
   int cluster_reduce;
   float *c_ptr;
   long long c_ld;
@@ -449,6 +454,15 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   TileFeed<CTA_GROUP == 2> feed{dynamic, cluster_id, num_clusters, total_work, ring_bar, ring_tile};
 
   // ---- set-up ---------------------------------------------------------------
+  // The kernel's parameters sit in the constant bank, cold at every launch, and a
+  // miss costs a few hundred clocks.  The producer lane would take those misses one
+  // after the other on its way to the first load (hints, split geometry, queue
+  // slot: different lines); warps that have nothing to do yet touch one line each
+  // now, in parallel, so the lines are there when the roles need them.
+  if (lane == 0 && warp >= 2 && warp < 6) {
+    const int touched = warp == 2 ? p.group_m : warp == 3 ? p.splits : warp == 4 ? p.c_rows : p.sched_slot_plus1;
+    asm volatile("" ::"r"(touched));
+  }
   if (threadIdx.x == 0) {
     *abort_ptr = 0;
     for (int s = 0; s < stages; s++) {
@@ -477,11 +491,50 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     ptx::tmem_alloc<CTA_GROUP>(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish<CTA_GROUP>();
   }
+  // What the producer lane needs before its first load and can work out from the
+  // kernel's parameters alone: the cache policies and where its first tile lies
+  // (a chain of integer divisions, about a microsecond for one thread).
+  struct ProducerTile {
+    int a_row0, b_row0, kb_begin, kb_end;
+  };
+  auto producer_tile = [&](int w) {
+    const int t = w / p.splits, sp = w - t * p.splits;
+    int tm, tn;
+    tile_coords(p, t, &tm, &tn);
+    ProducerTile r;
+    r.kb_begin = sp * p.kb_per_split;
+    r.kb_end = min(p.num_k_blocks, r.kb_begin + p.kb_per_split);
+    r.a_row0 = tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA;
+    r.b_row0 = tn * (NI * BN) + (int)cta_rank * (NI * B_ROWS);
+    return r;
+  };
+  uint64_t pol_a = 0, pol_b = 0;
+  ProducerTile first_tile{0, 0, 0, 0};
+  auto producer_preamble = [&]() {
+    auto policy = [](int h) {
+      return h == 1 ? ptx::l2_policy_evict_first() : h == 2 ? ptx::l2_policy_evict_last()
+                                                             : ptx::l2_policy_evict_normal();
+    };
+    pol_a = policy(p.hint_a);
+    pol_b = policy(p.hint_b);
+    // (the empty asm statements pin the arithmetic between the barrier arrival
+    // before this call and the wait after it: both are volatile asm too)
+    int first = cluster_id;
+    asm volatile("" : "+r"(first));
+    if (first < total_work) first_tile = producer_tile(first);
+    asm volatile("" : "+r"(first_tile.a_row0), "+r"(first_tile.b_row0), "+r"(first_tile.kb_begin), "+r"(first_tile.kb_end));
+  };
   ptx::tc_fence_before_sync();
   if constexpr (CTA_GROUP == 2) {
     __syncthreads();
-    // the peer's barriers must exist before anything arrives on them remotely
+    // The peer's barriers must exist before anything arrives on them remotely.
+    // The two CTAs of a pair do not start at the same instant: the producer lane
+    // does its arithmetic between its arrival and the wait, under that skew.
     ptx::cluster_arrive();
+    if (warp == 0) {
+      if (lane == 0) producer_preamble();
+      __syncwarp();
+    }
     ptx::cluster_wait();
   } else {
     // The producer warp needs nothing the other warps set up (its lane initialised
@@ -489,13 +542,32 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     // to its first loads, which are then in flight while the TMEM allocation and
     // this hand-off complete -- about a microsecond earlier, which a problem that
     // lasts tens of microseconds notices.
-    if (warp == 0) ptx::named_barrier_arrive(3u, kThreadsPerCta);
-    else ptx::named_barrier_sync(3u, kThreadsPerCta);
+    if (warp == 0) {
+      ptx::named_barrier_arrive(3u, kThreadsPerCta);
+      if (lane == 0) producer_preamble();
+      __syncwarp();
+    } else {
+      ptx::named_barrier_sync(3u, kThreadsPerCta);
+    }
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel's
+  // own parameters, so under a programmatic dependent launch it has overlapped the
+  // tail of the kernel before this one in the stream.  The roles that touch global
+  // memory (the producer: operands and the tile queue; the epilogue: C, C_in, bias)
+  // wait for that kernel themselves, as late as they can; the issuer works on
+  // shared memory and TMEM only and needs no wait of its own.
 
   // ---- roles ------------------------------------------------------------------
+  // cluster_reduce == 2: one cluster barrier phase separates the zeroing of the C
+  // tile (every epilogue warp of both CTAs, before it waits for its accumulator)
+  // from the first addition into it.  Every thread arrives exactly once; the
+  // producer and issuer warps arrive at once and collect the phase when their
+  // role is over.
+  bool reduce_add = false;
+  if constexpr (CTA_GROUP == 1 && MI == 1 && !OUT16 && !FANOUT && !AFFINE) reduce_add = p.cluster_reduce == 2;
+  if (reduce_add && warp < 2) ptx::cluster_arrive();
   if (warp == 0) {
     // ===== TMA producer (examples/kernels/gemm.ml:92-98 `prefetch`) =====
     if (lane == 0) {
@@ -505,11 +577,6 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      auto policy = [](int h) {
-        return h == 1 ? ptx::l2_policy_evict_first() : h == 2 ? ptx::l2_policy_evict_last()
-                                                               : ptx::l2_policy_evict_normal();
-      };
-      const uint64_t pol_a = policy(p.hint_a), pol_b = policy(p.hint_b);
       // The leader's lane owns the dynamic schedule: it announces this cluster's
       // tile n + 1 (taken from the queue) before it loads tile n, so the other
       // roles never wait for an index.  The peer CTA's lane reads the ring.
@@ -518,18 +585,18 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       if (announcer) feed.announce(0, cluster_id);
       int w = announcer ? cluster_id : feed.take(wctx);
       for (int n_local = 0; ok && w >= 0 && w < total_work; n_local++) {
+        const ProducerTile pt = (n_local == 0 && w == cluster_id) ? first_tile : producer_tile(w);
+        const int kb_begin = pt.kb_begin, kb_end = pt.kb_end, a_row0 = pt.a_row0, b_row0 = pt.b_row0;
+        if (n_local == 0) {
+          // first access to global memory (the queue, then the operands)
+          ptx::grid_dependency_wait();
+          ptx::grid_launch_dependents();
+        }
         int w_next = 0;
         if (announcer) {
           w_next = num_clusters + (int)atomicAdd(queue, 1u);
           feed.announce(n_local + 1, w_next);
         }
-        const int t = w / p.splits, sp = w - t * p.splits;
-        const int kb_begin = sp * p.kb_per_split;
-        const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
-        int tm, tn;
-        tile_coords(p, t, &tm, &tn);
-        const int a_row0 = tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA;
-        const int b_row0 = tn * (NI * BN) + (int)cta_rank * (NI * B_ROWS);
         for (int kb = kb_begin; kb < kb_end; kb++) {
           if (!bounded_wait(empty_bar + 8u * stage, phase ^ 1u, wctx, WAIT_EMPTY, (uint32_t)stage)) {
             ok = false;
@@ -723,6 +790,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     int local_tile = 0;
     const uint64_t pol_c = p.hint_c == 1 ? ptx::l2_policy_evict_first()
                            : p.hint_c == 2 ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_normal();
+    ptx::grid_dependency_wait();  // before anything of C, C_in or the bias is touched
     for (;; local_tile++) {
       // Every pass ends in the group's named barrier below, the last one
       // included: the four warps of a group leave the loop together or not at
@@ -733,6 +801,37 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       const int set = local_tile % SETS;
       const uint32_t set_phase = (uint32_t)(local_tile / SETS) & 1u;
       const int unit = set * U + mi;
+      // where the tile goes: worked out before the wait, not between the
+      // accumulator becoming ready and the first TMEM load
+      int tm = 0, tn = 0, sp = 0;
+      if (valid) {
+        const int t = w / p.splits;
+        sp = w - t * p.splits;
+        tile_coords(p, t, &tm, &tn);
+      }
+      const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
+                        (MI == 2 ? mi * 128 : 0) + quad * 32;
+      if (reduce_add && local_tile == 0) {
+        // Zero this warp's part of the C tile (its 32 rows): K slice 0 takes the even
+        // 32-column chunks, slice 1 the odd ones.  Ordinary stores, four whole
+        // 128-byte rows per instruction; the proxy fence orders them before the TMA
+        // reductions that follow the barrier.
+        if (valid) {
+          for (int c = 0; c < CHUNKS_PER_GROUP; c++) {
+            if (((ch_begin + c) & 1) != (sp & 1)) continue;
+            const int col = tn * BN + (ch_begin + c) * 32 + 4 * (lane & 7);
+            if (col >= p.c_cols) continue;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const int row = c_row + 4 * j + (lane >> 3);
+              if (row < p.c_rows) ptx::st_global_v4_zero(p.c_ptr + (size_t)row * (size_t)p.c_ld + col);
+            }
+          }
+          ptx::fence_proxy_async_global();
+          __syncwarp();
+        }
+        ptx::cluster_arrive();
+      }
       bool stop = !valid;
       if (valid && (ew & 3) == 0 && lane == 0)
         stop = !bounded_wait(tmem_full_bar + 8u * unit, set_phase, wctx, WAIT_TMEM_FULL, (uint32_t)w);
@@ -742,11 +841,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       // barrier, which issues nothing, and its OR hands all 128 threads the same
       // verdict.
       if (ptx::named_barrier_or(1u + (uint32_t)group, 128u, stop)) break;
-      const int t = w / p.splits, sp = w - t * p.splits;
-      int tm, tn;
-      tile_coords(p, t, &tm, &tn);
-      const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
-                        (MI == 2 ? mi * 128 : 0) + quad * 32;
+      if (reduce_add) ptx::cluster_wait();  // the whole tile of C is zero, in both CTAs' view
       // first column in C of this warp's chunk c (32 accumulator columns)
       auto chunk_col = [&](int c) {
         const int j = (ch_begin + c) * 32;
@@ -757,7 +852,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                               (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
       if constexpr (CTA_GROUP == 1 && MI == 1) {
-        if (p.cluster_reduce) {
+        if (p.cluster_reduce == 1) {
           // Leave this CTA's partial tile in its own shared memory, in the (now
           // idle) operand ring: row r at r * BN * 4 bytes, 16-byte pieces
           // XOR-swizzled by r % 8 inside each 128-byte group.
@@ -825,6 +920,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
               // every destination's store has read it
               for (int d = 0; d < p.n_dests; d++)
                 ptx::tma_store_2d_hint(&p.dest_maps[d], chunk_col(c), c_row, buf, pol_c);
+            } else if (reduce_add) {
+              ptx::tma_reduce_add_2d(map_c, chunk_col(c), c_row, buf);
             } else {
               ptx::tma_store_2d_hint(map_c, chunk_col(c), c_row, buf, pol_c);
             }
@@ -891,10 +988,14 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     if (lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
   }
+  if (reduce_add && warp < 2) {
+    __syncwarp();
+    ptx::cluster_wait();
+  }
 
   // ---- split-K reduction across the cluster --------------------------------------
   if constexpr (CTA_GROUP == 1 && MI == 1) {
-    if (p.cluster_reduce) {
+    if (p.cluster_reduce == 1) {
       // Every thread of every CTA passes both cluster barriers, whatever
       // happened in its role (a timed-out wait included), so nobody is left
       // waiting; the data is only meaningful if no wait timed out, which the

@@ -376,6 +376,31 @@ def test_cluster_split_k(variant, splits, m, n, k):
         assert torch.equal(c.contiguous(), ws)
 
 
+@pytest.mark.parametrize("variant,m,n,k", [("cluster_splitk_128x128", 128, 1024, 4096), ("cluster_splitk_128x256", 200, 1000, 2112),
+                                           ("cluster_splitk_128x128", 1024, 1024, 8192)])
+def test_two_slice_cluster_split_k_both_routes_agree(monkeypatch, variant, m, n, k):
+    """Two K slices in a cluster are summed either by TMA reductions into a tile of
+    C that the kernel zeroed first (the default) or through distributed shared
+    memory (what four and eight slices use).  Two addends: the same bits either
+    way, over whatever C held before (NaN here), and nothing outside C."""
+    rng = np.random.default_rng(k + m)
+    a_bits, bt_bits = rand_bf16(rng, m, k, 0.02), rand_bf16(rng, n, k, 0.02)
+    a, bt = bf16_tensor(a_bits), bf16_tensor(bt_bits)
+    flags = gemm.make_flags(variant, splits=2)
+    out = {}
+    for route in ("", "dsmem"):
+        monkeypatch.setenv("OXGPU_CLUSTER_REDUCE", route)
+        pad = torch.full((m + 2, n + 8), float("nan"), device=DEV)
+        c = pad[1:m + 1, 4:n + 4]
+        for _ in range(3):   # repeated launches into the same C: the zeroing is part of every launch
+            gemm.gemm_bf16(a, bt, c, flags=flags)
+        out[route] = c.contiguous()
+        assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
+        assert torch.isnan(pad[:, :4]).all() and torch.isnan(pad[:, n + 4:]).all()
+    assert torch.equal(out[""], out["dsmem"])
+    check_bf16(a_bits, bt_bits, out[""])
+
+
 def test_skinny_problem_takes_the_cluster_split_k_path_by_default():
     a = torch.empty(128, 8192, device=DEV, dtype=torch.bfloat16)
     bt = torch.empty(8192, 8192, device=DEV, dtype=torch.bfloat16)
@@ -906,6 +931,47 @@ def test_launches_can_be_captured_in_a_cuda_graph():
         for _, _, _, eager, eager_affine, outs in cases:
             assert torch.equal(outs[0], eager) and torch.equal(outs[1], eager)
             assert torch.equal(outs[2], eager_affine)
+
+
+@pytest.mark.parametrize("size", [256, 1024])
+def test_back_to_back_launches_see_each_others_results(monkeypatch, size):
+    """The GEMM kernels are launched so that each may start its set-up while the
+    kernel before it is still running; everything that touches global memory waits
+    for that kernel first.  A chain in which every GEMM reads the one before it
+    (bf16 C of one is the A of the next), and a C that consecutive launches
+    overwrite, must give what the same calls give as ordinary launches with a
+    synchronisation after each.  Small problems: a few CTAs each, so the next
+    kernel's CTAs really do start on idle SMs while the previous one runs."""
+    n = size
+    x0 = torch.empty(n, n, device=DEV, dtype=torch.bfloat16)
+    gemm.fill_normal(x0, 41, 1.0, 0)
+    ws = []
+    for i in range(6):
+        w = torch.empty(n, n, device=DEV, dtype=torch.bfloat16)
+        gemm.fill_normal(w, 42 + i, 1.0 / n ** 0.5, 0)
+        ws.append(w)
+
+    def chain(sync):
+        x = x0
+        for w in ws:                      # x <- x W^T, six times, each reading the last
+            x = gemm.gemm_bf16_out16(x, w)
+            if sync:
+                torch.cuda.synchronize()
+        out = torch.full((n, n), float("nan"), device=DEV)
+        for w in ws:                      # the same C written six times: the last one stays
+            gemm.gemm_bf16(x, w, out)
+            if sync:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return x, out
+
+    monkeypatch.setenv("OXGPU_DEPENDENT_LAUNCH", "0")
+    want_x, want_out = chain(True)
+    monkeypatch.setenv("OXGPU_DEPENDENT_LAUNCH", "1")
+    for _ in range(5):
+        got_x, got_out = chain(False)
+        assert torch.equal(got_x.view(torch.int16), want_x.view(torch.int16))
+        assert torch.equal(got_out, want_out)
 
 
 def test_single_tile_row_problems_do_not_take_tall_tiles():
