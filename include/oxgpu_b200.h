@@ -146,6 +146,14 @@ OXGPU_API int oxgpu_b200_check_gpu_header(const oxgpu_gpu_header *header);
  * pure function of the linear tile id, the one the persistent scheduler uses. */
 OXGPU_API int oxgpu_b200_grouped_tile(int pid, int group, int tiles_m, int tiles_n, int *tile_m,
                                       int *tile_n);
+/* The order in which the GEMM kernels of this library visit tiles: the grouped
+ * order above, with the columns of every other group of tile rows walked in
+ * reverse (the B^T panels used last in one group are used first in the next,
+ * while they are still in L2).  Computed with the multiply-by-reciprocal
+ * arithmetic the kernels use, so it also serves to check that arithmetic.  No
+ * counterpart in the reference, whose kernels walk the plain grouped order. */
+OXGPU_API int oxgpu_b200_tile_walk(int pid, int group, int tiles_m, int tiles_n, int *tile_m,
+                                   int *tile_n);
 
 /* ---- host launch layer: test/hardware/run_gemm_h100.cu, bench/bench.py -- */
 

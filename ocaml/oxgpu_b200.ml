@@ -24,6 +24,8 @@ external kernel_binding : tile_config -> string = "oxgpu_ml_kernel_binding"
 external choose_config_raw : int -> int -> int -> tile_config = "oxgpu_ml_choose_config"
 external kernel_info : string -> int * int * int = "oxgpu_ml_kernel_info"
 external grouped_tile : int -> int -> int -> int -> int * int = "oxgpu_ml_grouped_tile"
+(* the order this library's kernels visit tiles in (grouped, every other group of tile rows reversed) *)
+external tile_walk : int -> int -> int -> int -> int * int = "oxgpu_ml_tile_walk"
 
 let choose_config ?(m = 4096) ?(n = 4096) ?(k = 4096) () = choose_config_raw m n k
 

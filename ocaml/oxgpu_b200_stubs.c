@@ -94,6 +94,17 @@ CAMLprim value oxgpu_ml_grouped_tile(value pid, value group, value tm, value tn)
   CAMLreturn(r);
 }
 
+CAMLprim value oxgpu_ml_tile_walk(value pid, value group, value tm, value tn) {
+  CAMLparam4(pid, group, tm, tn);
+  CAMLlocal1(r);
+  int m, n;
+  check(oxgpu_b200_tile_walk(Int_val(pid), Int_val(group), Int_val(tm), Int_val(tn), &m, &n));
+  r = caml_alloc_tuple(2);
+  Store_field(r, 0, Val_int(m));
+  Store_field(r, 1, Val_int(n));
+  CAMLreturn(r);
+}
+
 CAMLprim value oxgpu_ml_gemm_tmap(value name, value a, value b, value c, value m, value n,
                                   value k, value stream) {
   CAMLparam5(name, a, b, c, m);

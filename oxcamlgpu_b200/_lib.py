@@ -69,6 +69,7 @@ def lib() -> ctypes.CDLL:
         "oxgpu_b200_parse_gpu_header": ([c_char_p, sz, ctypes.POINTER(GpuHeaderStruct)], c_int),
         "oxgpu_b200_check_gpu_header": ([ctypes.POINTER(GpuHeaderStruct)], c_int),
         "oxgpu_b200_grouped_tile": ([c_int, c_int, c_int, c_int, intp, intp], c_int),
+        "oxgpu_b200_tile_walk": ([c_int, c_int, c_int, c_int, intp, intp], c_int),
         "oxgpu_b200_encode_tmap_2d": ([c_void_p, c_void_p, c_int, u64, u64, u64, u32, u32], c_int),
         "oxgpu_b200_gemm_tmap": ([c_char_p, u64, u64, u64, c_int, c_int, c_int, c_void_p], c_int),
         "oxgpu_b200_gemm_tf32": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, i64, i64, i64,

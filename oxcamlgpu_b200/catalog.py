@@ -150,6 +150,14 @@ def grouped_tile(pid: int, group: int, tiles_m: int, tiles_n: int) -> tuple[int,
     return tm.value, tn.value
 
 
+def tile_walk(pid: int, group: int, tiles_m: int, tiles_n: int) -> tuple[int, int]:
+    """Tile `pid` of the order the library's kernels visit tiles in: grouped_tile
+    with the columns of every other group of tile rows reversed."""
+    tm, tn = ctypes.c_int(), ctypes.c_int()
+    _invalid(lib().oxgpu_b200_tile_walk, pid, group, tiles_m, tiles_n, ctypes.byref(tm), ctypes.byref(tn))
+    return tm.value, tn.value
+
+
 TYPE_NAMES = {1: "scalar_i32", 2: "scalar_f32", 3: "bool", 4: "unit", 5: "buffer_f32", 6: "buffer_bf16",
               7: "buffer_f16", 8: "tensor_map", 9: "scalar_u64"}
 OWNERSHIP_NAMES = {1: "unique", 2: "aliased"}

@@ -343,6 +343,10 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
 
   const long long work = (long long)p.tiles_m * p.tiles_n * p.splits;
   if (work <= 0 || work > 0x7fffffffLL) return fail(OXGPU_E_TOO_LARGE, "too many tiles");
+  if ((long long)p.group_m * p.tiles_n > 0x7fffffffLL) return fail(OXGPU_E_TOO_LARGE, "too many tiles in a group of tile rows");
+  p.div_splits = make_fast_divisor(p.splits, work);
+  p.div_per_group = make_fast_divisor(p.group_m * p.tiles_n, work);
+  p.div_group = make_fast_divisor(p.group_m, work);
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreadsPerCta, 1, 1);

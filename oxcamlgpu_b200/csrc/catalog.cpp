@@ -424,4 +424,18 @@ int oxgpu_b200_grouped_tile(int pid, int group, int tiles_m, int tiles_n, int *t
   return OXGPU_OK;
 }
 
+// The kernels' own walk: grouped_tile with the columns of every other group of
+// tile rows reversed, through the reciprocal arithmetic the kernels use.
+int oxgpu_b200_tile_walk(int pid, int group, int tiles_m, int tiles_n, int *tile_m, int *tile_n) {
+  if (!tile_m || !tile_n || group <= 0 || tiles_m <= 0 || tiles_n <= 0 || pid < 0 ||
+      (long long)pid >= (long long)tiles_m * tiles_n || (long long)group * tiles_n > 0x7fffffffLL)
+    return fail(OXGPU_E_INVALID_ARG, "tile_walk: argument out of range");
+  const long long work = (long long)tiles_m * tiles_n;
+  const FastDivisor per_group = make_fast_divisor(group * tiles_n, work), by_group = make_fast_divisor(group, work);
+  int group_index;
+  grouped_tile_fast(pid, per_group, by_group, tiles_m, tile_m, tile_n, &group_index);
+  if (group_index & 1) *tile_n = tiles_n - 1 - *tile_n;
+  return OXGPU_OK;
+}
+
 }  // extern "C"

@@ -120,4 +120,45 @@ OXGPU_HD inline void grouped_tile(int pid, int group, int tiles_m, int tiles_n, 
   *tile_n = (pid % per_group) / rows;
 }
 
+// Division by a number that is fixed for a whole launch, for the kernels' tile
+// arithmetic: an integer division costs one thread about 200 clocks, and the
+// producer lane does several in a row before its first load.  magic =
+// floor(2^40 / d) + 1 gives floor(a / d) = (a * magic) >> 40 exactly whenever
+// a * d < 2^40 (the excess over a / d is below 1 / d); make_fast_divisor returns
+// magic = 0, meaning "divide", when the largest dividend does not allow that.
+struct FastDivisor {
+  unsigned long long magic;
+  int d;
+  int pad;
+};
+OXGPU_HD inline FastDivisor make_fast_divisor(int d, long long max_dividend) {
+  FastDivisor f{0ull, d, 0};
+  if (d > 0 && max_dividend >= 0 && max_dividend < (1ll << 22) && (long long)d < (1ll << 18))
+    f.magic = (1ull << 40) / (unsigned long long)d + 1ull;
+  return f;
+}
+OXGPU_HD inline int fast_div(int a, const FastDivisor &f) {
+  return f.magic ? (int)(((unsigned long long)(unsigned)a * f.magic) >> 40) : a / f.d;
+}
+
+// grouped_tile with the launch's divisors prepared (per_group = group * tiles_n),
+// plus the index of the group of tile rows the tile lies in.  Same results as
+// grouped_tile for every pid in [0, tiles_m * tiles_n).
+OXGPU_HD inline void grouped_tile_fast(int pid, const FastDivisor &per_group, const FastDivisor &group, int tiles_m,
+                                       int *tile_m, int *tile_n, int *group_index) {
+  const int q = fast_div(pid, per_group);
+  const int r = pid - q * per_group.d;
+  const int first = q * group.d;
+  *group_index = q;
+  if (tiles_m - first >= group.d) {  // a full group: pid % rows == r % group
+    const int col = fast_div(r, group);
+    *tile_n = col;
+    *tile_m = first + (r - col * group.d);
+  } else {  // the last, shorter group of tile rows
+    const int rows = tiles_m - first;
+    *tile_m = first + pid % rows;
+    *tile_n = r / rows;
+  }
+}
+
 }  // namespace oxgpu

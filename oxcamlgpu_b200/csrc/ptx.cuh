@@ -50,6 +50,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+// Arrival without release semantics, for the start-up hand-shake only: what the
+// peer must see there are the mbarrier initialisations, which their own fence
+// (fence_mbar_init, release at cluster scope) publishes; a releasing arrival
+// costs several hundred clocks more.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }

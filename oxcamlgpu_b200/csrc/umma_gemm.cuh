@@ -109,6 +109,8 @@ struct GemmParams {
   // dynamic -- after its first tile a cluster takes the next tile nobody has
   // started from queue slot s of g_tile_queue (see TileFeed).
   int sched_slot_plus1;
+  // splits, group_m * tiles_n and group_m with their reciprocals (see FastDivisor)
+  FastDivisor div_splits, div_per_group, div_group;
 };
 
 // Parameters of the fan-out kernels: the epilogue writes every staged 32x32
@@ -132,8 +134,14 @@ struct GemmParamsFanout : GemmParams {
 // 8192 with a cold L2: 3.13 -> 2.97 ms; no effect at 8192^3, where a group is
 // a third of the problem).  Which SM computes a tile does not change its value.
 __device__ __forceinline__ void tile_coords(const GemmParams &p, int t, int *tm, int *tn) {
-  grouped_tile(t, p.group_m, p.tiles_m, p.tiles_n, tm, tn);
-  if ((*tm / p.group_m) & 1) *tn = p.tiles_n - 1 - *tn;
+  int group_index;
+  grouped_tile_fast(t, p.div_per_group, p.div_group, p.tiles_m, tm, tn, &group_index);
+  if (group_index & 1) *tn = p.tiles_n - 1 - *tn;
+}
+// work item -> (tile, K slice)
+__device__ __forceinline__ void split_work(const GemmParams &p, int w, int *t, int *sp) {
+  *t = fast_div(w, p.div_splits);
+  *sp = w - *t * p.splits;
 }
 
 struct WaitCtx {
@@ -459,8 +467,16 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   // after the other on its way to the first load (hints, split geometry, queue
   // slot: different lines); warps that have nothing to do yet touch one line each
   // now, in parallel, so the lines are there when the roles need them.
-  if (lane == 0 && warp >= 2 && warp < 6) {
-    const int touched = warp == 2 ? p.group_m : warp == 3 ? p.splits : warp == 4 ? p.c_rows : p.sched_slot_plus1;
+  if (lane == 0 && warp >= 2) {
+    // one field in every 32 bytes of the scalar part of the parameter block
+    const int touched = warp == 2   ? p.tiles_m
+                        : warp == 3 ? p.splits
+                        : warp == 4 ? p.c_rows
+                        : warp == 5 ? __float_as_int(p.alpha)
+                        : warp == 6 ? p.sched_slot_plus1
+                        : warp == 7 ? p.div_per_group.d
+                        : warp == 8 ? p.div_group.d
+                                    : p.hint_a;
     asm volatile("" ::"r"(touched));
   }
   if (threadIdx.x == 0) {
@@ -498,8 +514,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     int a_row0, b_row0, kb_begin, kb_end;
   };
   auto producer_tile = [&](int w) {
-    const int t = w / p.splits, sp = w - t * p.splits;
-    int tm, tn;
+    int t, sp, tm, tn;
+    split_work(p, w, &t, &sp);
     tile_coords(p, t, &tm, &tn);
     ProducerTile r;
     r.kb_begin = sp * p.kb_per_split;
@@ -510,18 +526,18 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   };
   uint64_t pol_a = 0, pol_b = 0;
   ProducerTile first_tile{0, 0, 0, 0};
-  auto producer_preamble = [&]() {
+  auto producer_preamble = [&]() {  // producer lane only
     auto policy = [](int h) {
       return h == 1 ? ptx::l2_policy_evict_first() : h == 2 ? ptx::l2_policy_evict_last()
                                                              : ptx::l2_policy_evict_normal();
     };
-    pol_a = policy(p.hint_a);
-    pol_b = policy(p.hint_b);
     // (the empty asm statements pin the arithmetic between the barrier arrival
     // before this call and the wait after it: both are volatile asm too)
     int first = cluster_id;
     asm volatile("" : "+r"(first));
     if (first < total_work) first_tile = producer_tile(first);
+    pol_a = policy(p.hint_a);
+    pol_b = policy(p.hint_b);
     asm volatile("" : "+r"(first_tile.a_row0), "+r"(first_tile.b_row0), "+r"(first_tile.kb_begin), "+r"(first_tile.kb_end));
   };
   ptx::tc_fence_before_sync();
@@ -530,7 +546,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
     // The peer's barriers must exist before anything arrives on them remotely.
     // The two CTAs of a pair do not start at the same instant: the producer lane
     // does its arithmetic between its arrival and the wait, under that skew.
-    ptx::cluster_arrive();
+    ptx::cluster_arrive_relaxed();
     if (warp == 0) {
       if (lane == 0) producer_preamble();
       __syncwarp();
@@ -584,8 +600,13 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       unsigned int *const queue = g_tile_queue + 2 * (dynamic ? p.sched_slot_plus1 - 1 : 0);
       if (announcer) feed.announce(0, cluster_id);
       int w = announcer ? cluster_id : feed.take(wctx);
+      // The first tile of every CTA is tile `cluster_id` (static walk, or the one the
+      // leader announced first); its coordinates come from the set-up.  Those of each
+      // later tile are worked out right after the loads of the tile before it have
+      // been issued, while they are in flight.
+      ProducerTile pt = first_tile;
+      if (w >= 0 && w < total_work && w != cluster_id) pt = producer_tile(w);
       for (int n_local = 0; ok && w >= 0 && w < total_work; n_local++) {
-        const ProducerTile pt = (n_local == 0 && w == cluster_id) ? first_tile : producer_tile(w);
         const int kb_begin = pt.kb_begin, kb_end = pt.kb_end, a_row0 = pt.a_row0, b_row0 = pt.b_row0;
         if (n_local == 0) {
           // first access to global memory (the queue, then the operands)
@@ -629,6 +650,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           }
         }
         w = announcer ? w_next : feed.take(wctx);
+        if (w >= 0 && w < total_work) pt = producer_tile(w);
       }
       if (w < 0) ok = false;
       if (!ok || *abort_ptr) {
@@ -689,7 +711,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
           ok = false;
           break;
         }
-        const int sp = w % p.splits;
+        int t_of_w, sp;
+        split_work(p, w, &t_of_w, &sp);
         const int kb_begin = sp * p.kb_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.kb_per_split);
         const int set = local_tile % SETS;
@@ -805,8 +828,8 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       // accumulator becoming ready and the first TMEM load
       int tm = 0, tn = 0, sp = 0;
       if (valid) {
-        const int t = w / p.splits;
-        sp = w - t * p.splits;
+        int t;
+        split_work(p, w, &t, &sp);
         tile_coords(p, t, &tm, &tn);
       }
       const int c_row = sp * p.split_row_stride + tm * (BM_CTA * CTA_GROUP) + (int)cta_rank * BM_CTA +
@@ -842,6 +865,18 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       // verdict.
       if (ptx::named_barrier_or(1u + (uint32_t)group, 128u, stop)) break;
       if (reduce_add) ptx::cluster_wait();  // the whole tile of C is zero, in both CTAs' view
+      // The last tile of this CTA (static walk), single accumulator unit: its UMMAs
+      // are all complete, no load is in flight or will be issued, so the operand
+      // ring is free.  Each 32-column chunk then gets a staging buffer of its own
+      // there (at most four per warp with these tiles) and no chunk waits for the
+      // TMA store before it to have read its source: what a problem of one tile per
+      // CTA sees of the epilogue is a chain of store latencies otherwise.
+      bool spread = false;
+      if constexpr (U == 1 && CHUNKS_PER_GROUP <= 4)
+        spread = !dynamic && w + num_clusters >= total_work && (uint32_t)stages * STAGE_BYTES >= 8u * 3u * 4096u;
+      auto chunk_buf = [&](int c) {  // staging buffer of the c-th chunk this warp handles
+        return spread && c > 0 ? smem_base + (uint32_t)(ew * 3 + (c - 1)) * 4096u : buf;
+      };
       // first column in C of this warp's chunk c (32 accumulator columns)
       auto chunk_col = [&](int c) {
         const int j = (ch_begin + c) * 32;
@@ -899,18 +934,21 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
             if (c + 1 < CHUNKS_PER_GROUP) affine_fetch_rows((c & 1) ? cin_a : cin_b, p, c_row, chunk_col(c + 1), lane);
           }
           // the previous store must be done reading the staging buffer
-          if (lane == 0) ptx::tma_store_wait_read<0>();
-          __syncwarp();
+          const uint32_t cbuf = chunk_buf(c), crow = cbuf + (uint32_t)lane * 128u;
+          if (!spread || c == 0) {
+            if (lane == 0) ptx::tma_store_wait_read<0>();
+            __syncwarp();
+          }
           // row `lane` of the 32x32 sub-tile, 16-byte chunks XOR-swizzled by
           // (row % 8) as the 128-byte-swizzle store map expects
 #pragma unroll
           for (int j = 0; j < 8; j++) {
-            ptx::st_shared_v4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
+            ptx::st_shared_v4(crow + (uint32_t)((j ^ (lane & 7)) << 4), cur[4 * j], cur[4 * j + 1],
                               cur[4 * j + 2], cur[4 * j + 3]);
           }
           if constexpr (AFFINE) {
             __syncwarp();  // the whole sub-tile is staged: transform it in place, four rows per instruction
-            affine_apply_staged(buf, (c & 1) ? cin_b : cin_a, p, chunk_col(c), lane);
+            affine_apply_staged(cbuf, (c & 1) ? cin_b : cin_a, p, chunk_col(c), lane);
           }
           ptx::fence_proxy_async_smem();
           __syncwarp();
@@ -919,11 +957,11 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
               // one bulk group per sub-tile: the staging buffer is reused once
               // every destination's store has read it
               for (int d = 0; d < p.n_dests; d++)
-                ptx::tma_store_2d_hint(&p.dest_maps[d], chunk_col(c), c_row, buf, pol_c);
+                ptx::tma_store_2d_hint(&p.dest_maps[d], chunk_col(c), c_row, cbuf, pol_c);
             } else if (reduce_add) {
-              ptx::tma_reduce_add_2d(map_c, chunk_col(c), c_row, buf);
+              ptx::tma_reduce_add_2d(map_c, chunk_col(c), c_row, cbuf);
             } else {
-              ptx::tma_store_2d_hint(map_c, chunk_col(c), c_row, buf, pol_c);
+              ptx::tma_store_2d_hint(map_c, chunk_col(c), c_row, cbuf, pol_c);
             }
             ptx::tma_store_commit();
           }

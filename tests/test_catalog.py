@@ -168,6 +168,30 @@ def _gpu_text(kernel="gemm_fast", threads=288, args=None, fmt="3", result=True, 
     return "\n".join(rows) + "\n"
 
 
+@pytest.mark.parametrize("tiles_m,tiles_n,group", [(1, 1, 16), (16, 32, 4), (17, 5, 4), (3, 700, 8), (64, 256, 4), (7, 3, 16),
+                                                    (1, 2048, 16), (2048, 2047, 16)])
+def test_tile_walk_is_grouped_tile_with_every_other_group_reversed(oxlib, tiles_m, tiles_n, group):
+    """The kernels' walk goes through multiply-by-reciprocal arithmetic (magic
+    numbers for the launch's divisors, plain division for the last, shorter group
+    of tile rows, and for tile counts too large for the reciprocal to be exact --
+    the 2048 x 2047 case): it must agree with the reference's grouped order,
+    columns reversed in odd groups, for every tile."""
+    total = tiles_m * tiles_n
+    pids = range(total) if total <= 20000 else list(range(0, total, 997)) + [total - 1, total - 2]
+    seen = set()
+    for pid in pids:
+        tm, tn = cat.grouped_tile(pid, group, tiles_m, tiles_n)
+        if (tm // group) & 1:
+            tn = tiles_n - 1 - tn
+        assert cat.tile_walk(pid, group, tiles_m, tiles_n) == (tm, tn)
+        seen.add((tm, tn))
+    if total <= 20000:
+        assert len(seen) == total
+    with pytest.raises(Exception):
+        cat.tile_walk(total, group, tiles_m, tiles_n)
+
+
+
 def test_gpu_header_round_trip_and_check(oxlib):
     h = cat.parse_gpu_header(_gpu_text())
     assert h.kernel == "gemm_fast" and h.threads == 288 and len(h.args) == 6
