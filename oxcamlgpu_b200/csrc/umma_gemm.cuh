@@ -16,7 +16,8 @@
 //                                 of four warps, one warp per TMEM lane quadrant)
 //
 // The kernel is persistent: each CTA (or CTA pair) walks tiles
-// first, first+stride, ... in the grouped order.  Where the tile's accumulator
+// first, first+stride, ... in the grouped order, or, on problems of many tiles,
+// takes the next tile of that order from a queue (TileFeed).  Where the tile's accumulator
 // takes at most half of TMEM, two accumulator sets alternate so the epilogue of
 // tile i overlaps the main loop of tile i+1; the largest tile (256 rows x 256
 // columns per CTA) fills TMEM and trades that overlap for a quarter less
@@ -24,11 +25,14 @@
 // stages its own rows of A and its own half of the B^T rows, the leader CTA
 // issues UMMAs that read both CTAs' shared memory, and no load is multicast.
 //
-// Every wait is bounded: when a wait outlives its budget the waiter records
-// where it gave up in the device status block, raises the CTA's abort flag and
-// all roles leave through the common teardown (pending loads/stores drained,
-// TMEM released).  The reference's waits spin forever
-// (lib/backend/ptx.ml:174-181).
+// Every mbarrier wait is bounded: when a wait outlives its budget the waiter
+// records where it gave up in the device status block, raises the CTA's abort
+// flag and all roles leave through the common teardown (pending loads/stores
+// drained, TMEM released).  The reference's waits spin forever
+// (lib/backend/ptx.ml:174-181).  The hardware barriers (CTA, named, cluster)
+// are placed where every thread they count reaches them whatever its waits
+// returned, and `griddepcontrol.wait` ends when the kernel before this one in
+// the stream does.
 #pragma once
 
 #include <cuda.h>
