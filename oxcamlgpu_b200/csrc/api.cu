@@ -283,6 +283,8 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
   const int most = variant_max_stages(plan.variant);
   if (stages <= 0 || stages > most) stages = most;
   if (stages < 2) stages = 2;
+  if (plan.cluster_splits > 1 && (plan.affine || plan.fanout || plan.out16))
+    return fail(OXGPU_E_INVALID_ARG, "in-cluster split-K exists for the plain f32-output kernels only");
   if (plan.cluster_splits > 1) {
     // the partial tile (128 rows x tile_n f32) is parked in the operand ring
     const int need = 128 * shape.tile_n * 4, per = variant_stage_bytes(plan.variant);

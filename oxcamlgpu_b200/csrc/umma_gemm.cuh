@@ -586,7 +586,9 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   // producer and issuer warps arrive at once and collect the phase when their
   // role is over.
   bool reduce_add = false;
-  if constexpr (CTA_GROUP == 1 && MI == 1 && !OUT16 && !FANOUT && !AFFINE) reduce_add = p.cluster_reduce == 2;
+  // (only the plain one-CTA 128-row kernels are ever launched as split-K clusters)
+  constexpr bool CLUSTER_SPLIT_CAPABLE = CTA_GROUP == 1 && MI == 1 && !OUT16 && !FANOUT && !AFFINE;
+  if constexpr (CLUSTER_SPLIT_CAPABLE) reduce_add = p.cluster_reduce == 2;
   if (reduce_add && warp < 2) ptx::cluster_arrive();
   if (warp == 0) {
     // ===== TMA producer (examples/kernels/gemm.ml:92-98 `prefetch`) =====
@@ -890,7 +892,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
       ptx::tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
                               (uint32_t)(set * ACC_COLS + mi * BN + ch_begin * 32);
-      if constexpr (CTA_GROUP == 1 && MI == 1) {
+      if constexpr (CLUSTER_SPLIT_CAPABLE) {
         if (p.cluster_reduce == 1) {
           // Leave this CTA's partial tile in its own shared memory, in the (now
           // idle) operand ring: row r at r * BN * 4 bytes, 16-byte pieces
@@ -1036,7 +1038,7 @@ umma_gemm_kernel(const __grid_constant__ typename std::conditional<FANOUT, GemmP
   }
 
   // ---- split-K reduction across the cluster --------------------------------------
-  if constexpr (CTA_GROUP == 1 && MI == 1) {
+  if constexpr (CLUSTER_SPLIT_CAPABLE) {
     if (p.cluster_reduce == 1) {
       // Every thread of every CTA passes both cluster barriers, whatever
       // happened in its role (a timed-out wait included), so nobody is left

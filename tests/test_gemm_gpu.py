@@ -360,9 +360,11 @@ def test_split_k(m, n, k, splits):
                                             ("cluster_splitk_128x256", 8), ("cluster_splitk_128x128", 0)])
 @pytest.mark.parametrize("m,n,k", [(128, 1024, 2048), (100, 520, 1000), (384, 512, 4096), (128, 256, 64)])
 def test_cluster_split_k(variant, splits, m, n, k):
-    """K slices across a thread-block cluster, summed through distributed shared
-    memory: same slices and summation order as the workspace split-K, so the
-    two agree bit for bit; ragged edges and NaN guard bands as elsewhere."""
+    """K slices across a thread-block cluster (two: added by TMA reductions to a
+    tile of C that the kernel zeroes; four, eight: summed through distributed shared
+    memory in ascending order): same slices and summation order as the workspace
+    split-K, so the two agree bit for bit, and a second launch into the same C gives
+    the same bits again; ragged edges and NaN guard bands as elsewhere."""
     rng = np.random.default_rng(splits * 13 + k)
     a_bits, bt_bits = rand_bf16(rng, m, k, 0.02), rand_bf16(rng, n, k, 0.02)
     pad = torch.full((m + 2, n + 8), float("nan"), device=DEV)
@@ -371,9 +373,12 @@ def test_cluster_split_k(variant, splits, m, n, k):
     check_bf16(a_bits, bt_bits, c.contiguous())
     assert torch.isnan(pad[0]).all() and torch.isnan(pad[-1]).all()
     assert torch.isnan(pad[:, :4]).all() and torch.isnan(pad[:, n + 4:]).all()
+    first = c.contiguous().clone()
+    gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), c, flags=gemm.make_flags(variant, splits=splits))
+    assert torch.equal(c.contiguous(), first)         # a second launch into the same C: same bits
     if splits in (2, 4) and (k // 64) % splits == 0:
         ws = gemm.gemm_bf16(bf16_tensor(a_bits), bf16_tensor(bt_bits), flags=gemm.make_flags("splitk", splits=splits))
-        assert torch.equal(c.contiguous(), ws)
+        assert torch.equal(first, ws)
 
 
 @pytest.mark.parametrize("variant,m,n,k", [("cluster_splitk_128x128", 128, 1024, 4096), ("cluster_splitk_128x256", 200, 1000, 2112),
