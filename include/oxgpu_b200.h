@@ -157,6 +157,18 @@ OXGPU_API int oxgpu_b200_tile_walk(int pid, int group, int tiles_m, int tiles_n,
 
 /* ---- host launch layer: test/hardware/run_gemm_h100.cu, bench/bench.py -- */
 
+/* Environment variables the launch layer reads (at every launch, so a process
+ * may change them between calls); none is needed, all have defaults:
+ *   OXGPU_WAIT_BUDGET_MS=<n>      budget of every device-side wait (default 5000)
+ *   OXGPU_TILE_SCHEDULE=static    fixed-stride tile walk instead of the tile queue
+ *   OXGPU_DEPENDENT_LAUNCH=0      ordinary launches: without it a GEMM kernel may
+ *                                 start its set-up under the tail of the kernel
+ *                                 before it in the stream (it waits for that kernel
+ *                                 before it touches an operand or C)
+ *   OXGPU_CLUSTER_REDUCE=dsmem    two-slice in-cluster split-K summed through
+ *                                 distributed shared memory, not by TMA reductions
+ * Results do not depend on any of them. */
+
 /* encode_tiled_2d (test/hardware/run_gemm_h100.cu:46-72) /
  * encode_tensor_map_2d (bench/bench.py:126-147): 2-D tiled map, 128-byte
  * swizzle, L2 promotion 128 B, no out-of-bounds fill (zeros).  element_bytes 4
