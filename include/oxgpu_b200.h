@@ -206,10 +206,12 @@ enum {
   OXGPU_VARIANT_2CTA_512x256 = 7, /* CTA pair, 256 rows per CTA: two UMMA 256x256 per K step */
   OXGPU_VARIANT_1CTA_256x256 = 8, /* one CTA, two UMMA 128x256 sharing B */
   /* Split-K inside a thread-block cluster: the CTAs of a cluster take the K
-   * slices of one 128-row tile and sum them through distributed shared memory
-   * (no workspace, one kernel, fixed summation order).  For problems with too
-   * few tiles to fill the GPU; OXGPU_FLAG_SPLITS picks the cluster size (2, 4
-   * or 8; 0 = chosen by the library). */
+   * slices of one 128-row tile and sum them inside the kernel -- two slices by
+   * adding both partial tiles to a tile of C the kernel zeroes first (TMA
+   * reductions), four or eight through distributed shared memory in ascending
+   * order (no workspace, one kernel, the same bits at every launch).  For
+   * problems with too few tiles to fill the GPU; OXGPU_FLAG_SPLITS picks the
+   * cluster size (2, 4 or 8; 0 = chosen by the library). */
   OXGPU_VARIANT_CLUSTER_SPLITK_128x256 = 9,
   OXGPU_VARIANT_CLUSTER_SPLITK_128x128 = 10,
   /* CTA pair, 256 x 512 per pair: two UMMA 256x256 per K step sharing the staged
