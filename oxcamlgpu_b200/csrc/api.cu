@@ -401,6 +401,15 @@ int launch_umma(DeviceState &dev, const LaunchPlan &plan, GemmParams &p, int m, 
     long long ctas = work < sms ? work : sms;
     cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   }
+  // One wave (every tile has its own CTA or CTA pair, in-cluster split-K included):
+  // each operand byte is wanted by all its readers at about the same time and
+  // never again, so both operands are loaded evict-first.  Their lines then
+  // recycle among themselves instead of displacing what L2 held before the launch;
+  // when that is dirty (another kernel's output, or the bench's flush) its
+  // write-back would share HBM with the loads.  L2 flushed, 512 x 4096 x 4096: 26.0
+  // -> 23.0 us, 1024 x 1024 x 8192: 27.0 -> 24.8; no change on the other one-wave
+  // shapes measured (128 / 256 / 384 / 512 x 8192 x 8192, 2048^3, 128 x 4096 x 4096).
+  if (work <= (long long)cfg.gridDim.x / (plan.cluster_splits > 1 ? 1 : shape.cta_group)) p.hint_a = p.hint_b = 1;
   // Problems that keep every cluster busy for several tiles take their tiles
   // from a queue in walk order instead of a fixed stride, so the tiles in flight
   // stay a compact window of the walk (see TileFeed).  Split-K keeps the static
